@@ -1,0 +1,16 @@
+"""frisk_b200: B200 (sm_100a) GEMM and attention kernels behind the Frisk builder API.
+
+``import frisk_b200 as F`` offers what ``import frisk as F`` offers for the GEMM /
+attention path (``python/frisk/__init__.py:1-4``): the builder classes of
+``frisk_ffi.ir`` and the ``FriskHelper`` conveniences, plus ``execute`` /
+``attention_forward``, which run on the GPU through ``libfrisk_b200``.
+"""
+from . import capi, ir
+from .execute import attention_forward, attention_geometry, execute, gemm, gemm_plan
+from .helper import FriskHelper, create_context, create_session
+from .ir import (AffineMap, AllocBufferOp, BlockOp, CopyOp, FillOp, ForOp, GemmOp, GemmWarpPolicy, KernelOp,
+                 MemorySpace, OpState, ParallelOp, ReduceOp, block, builder, context, frisk, module, type, value)
+
+GLOBAL, SHARED, LOCAL = MemorySpace.GLOBAL, MemorySpace.SHARED, MemorySpace.LOCAL
+
+__all__ = [name for name in globals() if not name.startswith("_")]

@@ -1,0 +1,465 @@
+// C ABI of libfrisk_b200 (include/frisk_b200.h): context, host-side contract checks,
+// kernel selection, and the host-buffer entry points.
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+
+#include "common.cuh"
+
+namespace fb {
+
+// ---------------------------------------------------------------- TMA descriptor encode
+namespace {
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn get_encode() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+CUtensorMapDataType tmap_dtype(int dt) {
+  switch (dt) {
+    case FRISK_B200_F16: return CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    case FRISK_B200_BF16: return CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+    default: return CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+  }
+}
+}  // namespace
+
+int encode_tmap_2d(CUtensorMap* out, int dtype, const void* base, uint64_t inner, uint64_t outer,
+                   uint64_t outer_stride_bytes, uint32_t box_inner, uint32_t box_outer, bool swizzle128) {
+  EncodeTiledFn fn = get_encode();
+  if (!fn) return 999;
+  cuuint64_t dims[2] = {inner, outer};
+  cuuint64_t strides[1] = {outer_stride_bytes};
+  cuuint32_t box[2] = {box_inner, box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(out, tmap_dtype(dtype), 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return (int)r;
+}
+
+int encode_tmap_3d(CUtensorMap* out, int dtype, const void* base, uint64_t d0, uint64_t d1, uint64_t d2,
+                   uint64_t stride1_bytes, uint64_t stride2_bytes, uint32_t b0, uint32_t b1, uint32_t b2,
+                   bool swizzle128) {
+  EncodeTiledFn fn = get_encode();
+  if (!fn) return 999;
+  cuuint64_t dims[3] = {d0, d1, d2};
+  cuuint64_t strides[2] = {stride1_bytes, stride2_bytes};
+  cuuint32_t box[3] = {b0, b1, b2};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(out, tmap_dtype(dtype), 3, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return (int)r;
+}
+
+// ---------------------------------------------------------------- small kernels
+namespace {
+template <typename T>
+__global__ void convert_f32_kernel(const float* __restrict__ src, T* __restrict__ dst, int64_t n) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  // 8 elements per thread per step when everything is 16-byte aligned
+  int64_t n8 = n / 8;
+  if ((reinterpret_cast<uintptr_t>(src) & 15u) == 0 && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+    for (int64_t v = i; v < n8; v += stride) {
+      float4 a = __ldcs(reinterpret_cast<const float4*>(src) + 2 * v);
+      float4 b = __ldcs(reinterpret_cast<const float4*>(src) + 2 * v + 1);
+      T o[8] = {T(a.x), T(a.y), T(a.z), T(a.w), T(b.x), T(b.y), T(b.z), T(b.w)};
+      reinterpret_cast<uint4*>(dst)[v] = *reinterpret_cast<uint4*>(o);
+    }
+    for (int64_t k = n8 * 8 + i; k < n; k += stride) dst[k] = T(src[k]);
+  } else {
+    for (int64_t k = i; k < n; k += stride) dst[k] = T(src[k]);
+  }
+}
+}  // namespace
+
+int launch_convert_f32(const float* src, void* dst, int64_t n, int dtype, cudaStream_t s) {
+  if (n <= 0) return 0;
+  int blocks = (int)((n / 8 + 255) / 256);
+  if (blocks < 1) blocks = 1;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (dtype == FRISK_B200_F16)
+    convert_f32_kernel<__half><<<blocks, 256, 0, s>>>(src, static_cast<__half*>(dst), n);
+  else if (dtype == FRISK_B200_BF16)
+    convert_f32_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>(src, static_cast<__nv_bfloat16*>(dst), n);
+  else
+    return FRISK_B200_E_UNSUPPORTED;
+  return cudaGetLastError() == cudaSuccess ? 0 : FRISK_B200_E_CUDA;
+}
+
+// ---------------------------------------------------------------- helpers
+namespace {
+
+int ensure_stage(frisk_b200_ctx* ctx, int slot, size_t bytes, bool zero) {
+  StagingBuffer& b = ctx->stage[slot];
+  if (b.bytes >= bytes && b.ptr) return 0;
+  if (b.ptr) {
+    FB_CUDA(ctx, cudaFree(b.ptr));
+    b.ptr = nullptr;
+    b.bytes = 0;
+  }
+  size_t want = (bytes + 255) / 256 * 256;
+  FB_CUDA(ctx, cudaMalloc(&b.ptr, want));
+  b.bytes = want;
+  if (zero) FB_CUDA(ctx, cudaMemset(b.ptr, 0, want));
+  return 0;
+}
+
+bool ranges_overlap(const void* a, size_t an, const void* b, size_t bn) {
+  uintptr_t a0 = reinterpret_cast<uintptr_t>(a), b0 = reinterpret_cast<uintptr_t>(b);
+  return a0 < b0 + bn && b0 < a0 + an;
+}
+
+size_t operand_bytes(int64_t rows, int64_t cols, int64_t ld, size_t es) {
+  if (rows <= 0) return 0;
+  return (size_t)((rows - 1) * ld + cols) * es;
+}
+
+struct GemmExtents {
+  size_t a, b, c;
+};
+GemmExtents gemm_extents(const frisk_b200_gemm_desc& d) {
+  GemmDims g = resolve_dims(d);
+  size_t es = dtype_size(d.dtype_ab), cs = dtype_size(d.dtype_c);
+  GemmExtents e;
+  e.a = d.trans_a ? operand_bytes(g.K, g.M, g.lda, es) : operand_bytes(g.M, g.K, g.lda, es);
+  e.b = d.trans_b ? operand_bytes(g.N, g.K, g.ldb, es) : operand_bytes(g.K, g.N, g.ldb, es);
+  e.c = operand_bytes(g.M, g.N, g.ldc, cs);
+  return e;
+}
+
+}  // namespace
+}  // namespace fb
+
+using namespace fb;
+
+extern "C" {
+
+const char* frisk_b200_version(void) { return "frisk_b200 0.1 (sm_100a)"; }
+
+const char* frisk_b200_strerror(int code) {
+  switch (code) {
+    case FRISK_B200_OK: return "ok";
+    case FRISK_B200_E_GEMM_SHAPE: return "legacy-gemm-shape: A, B and C must be rank-2 with positive M, N, K and matching effective shapes";
+    case FRISK_B200_E_GEMM_TYPE: return "legacy-gemm-type: A and B must share an element type; C must match it or be f32 for f16/bf16 inputs";
+    case FRISK_B200_E_ALIGN: return "operand base address or row pitch is not 16-byte aligned";
+    case FRISK_B200_E_OVERLAP: return "output overlaps an input";
+    case FRISK_B200_E_WORKSPACE: return "workspace missing or too small";
+    case FRISK_B200_E_UNSUPPORTED: return "no kernel for this element type / layout / algorithm";
+    case FRISK_B200_E_ARG: return "invalid argument";
+    case FRISK_B200_E_ATTN_SHAPE: return "shape outside the attention launch contract";
+    case FRISK_B200_E_TOO_LARGE: return "problem exceeds the fixed capacity of this entry point";
+    case FRISK_B200_E_DEVICE_TIMEOUT: return "a bounded device-side wait ran out";
+    case FRISK_B200_E_CUDA: return "CUDA call failed";
+    default: return "unknown frisk_b200 status";
+  }
+}
+
+int frisk_b200_ctx_create(frisk_b200_ctx** out, int device) {
+  if (!out) return FRISK_B200_E_ARG;
+  *out = nullptr;
+  int count = 0;
+  if (cudaGetDeviceCount(&count) != cudaSuccess || device < 0 || device >= count) return FRISK_B200_E_CUDA;
+  frisk_b200_ctx* ctx = new frisk_b200_ctx();
+  ctx->device = device;
+  auto fail = [&](cudaError_t e) {
+    ctx->last_cuda = (int)e;
+    delete ctx;
+    return FRISK_B200_E_CUDA;
+  };
+  cudaError_t e;
+  if ((e = cudaSetDevice(device)) != cudaSuccess) return fail(e);
+  cudaDeviceProp prop;
+  if ((e = cudaGetDeviceProperties(&prop, device)) != cudaSuccess) return fail(e);
+  if (prop.major != 10) {  // sm_100a code only: fail loudly on anything else
+    delete ctx;
+    return FRISK_B200_E_UNSUPPORTED;
+  }
+  ctx->num_sms = prop.multiProcessorCount;
+  if ((e = cudaMalloc(&ctx->d_status, 256)) != cudaSuccess) return fail(e);
+  if ((e = cudaMemset(ctx->d_status, 0, 256)) != cudaSuccess) return fail(e);
+  if ((e = cudaMallocHost(&ctx->h_status, 256)) != cudaSuccess) return fail(e);
+  ctx->h_status[0] = 0;
+  if ((e = cudaStreamCreateWithFlags(&ctx->host_stream, cudaStreamNonBlocking)) != cudaSuccess) return fail(e);
+  if ((e = cudaStreamCreateWithFlags(&ctx->copy_stream, cudaStreamNonBlocking)) != cudaSuccess) return fail(e);
+  for (auto& ev : ctx->ev)
+    if ((e = cudaEventCreateWithFlags(&ev, cudaEventDisableTiming)) != cudaSuccess) return fail(e);
+  *out = ctx;
+  return 0;
+}
+
+int frisk_b200_ctx_destroy(frisk_b200_ctx* ctx) {
+  if (!ctx) return FRISK_B200_E_ARG;
+  cudaSetDevice(ctx->device);
+  cudaDeviceSynchronize();
+  for (auto& b : ctx->stage)
+    if (b.ptr) cudaFree(b.ptr);
+  if (ctx->d_status) cudaFree(ctx->d_status);
+  if (ctx->h_status) cudaFreeHost(ctx->h_status);
+  for (auto& ev : ctx->ev)
+    if (ev) cudaEventDestroy(ev);
+  if (ctx->host_stream) cudaStreamDestroy(ctx->host_stream);
+  if (ctx->copy_stream) cudaStreamDestroy(ctx->copy_stream);
+  delete ctx;
+  return 0;
+}
+
+int frisk_b200_last_status(frisk_b200_ctx* ctx) { return ctx ? ctx->last_status : FRISK_B200_E_ARG; }
+int frisk_b200_last_cuda(frisk_b200_ctx* ctx) { return ctx ? ctx->last_cuda : FRISK_B200_E_ARG; }
+
+int frisk_b200_check(frisk_b200_ctx* ctx, void* stream) {
+  if (!ctx) return FRISK_B200_E_ARG;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  FB_CUDA(ctx, cudaMemcpyAsync(ctx->h_status, ctx->d_status, sizeof(unsigned), cudaMemcpyDeviceToHost, s));
+  FB_CUDA(ctx, cudaStreamSynchronize(s));
+  ctx->last_status = (int)ctx->h_status[0];
+  if (ctx->last_status != 0) {
+    cudaMemsetAsync(ctx->d_status, 0, sizeof(unsigned), s);
+    cudaStreamSynchronize(s);
+    return FRISK_B200_E_DEVICE_TIMEOUT;
+  }
+  return 0;
+}
+
+// ------------------------------------------------------------------------------ GEMM
+int frisk_b200_gemm_validate(const frisk_b200_gemm_desc* d) {
+  if (!d) return FRISK_B200_E_ARG;
+  if (d->M <= 0 || d->N <= 0 || d->K <= 0) return FRISK_B200_E_GEMM_SHAPE;
+  if (!dtype_ok(d->dtype_ab) || !dtype_ok(d->dtype_c)) return FRISK_B200_E_GEMM_TYPE;
+  bool same = d->dtype_c == d->dtype_ab;
+  bool low_f32 = (d->dtype_ab == FRISK_B200_F16 || d->dtype_ab == FRISK_B200_BF16) && d->dtype_c == FRISK_B200_F32;
+  if (!same && !low_f32) return FRISK_B200_E_GEMM_TYPE;
+  GemmDims g = resolve_dims(*d);
+  int64_t a_cols = d->trans_a ? g.M : g.K, b_cols = d->trans_b ? g.K : g.N;
+  if (g.lda < a_cols || g.ldb < b_cols || g.ldc < g.N) return FRISK_B200_E_GEMM_SHAPE;
+  if (d->algo < FRISK_B200_ALGO_AUTO || d->algo > FRISK_B200_ALGO_SKINNY) return FRISK_B200_E_ARG;
+  return 0;
+}
+
+int frisk_b200_gemm_check_memrefs(int32_t a_rank, const int64_t* a_shape, int32_t a_dtype, int32_t b_rank,
+                                  const int64_t* b_shape, int32_t b_dtype, int32_t c_rank, const int64_t* c_shape,
+                                  int32_t c_dtype, int32_t trans_a, int32_t trans_b, int64_t m, int64_t n, int64_t k,
+                                  const char** message) {
+  const char* msg = nullptr;
+  int code = 0;
+  auto fail = [&](int c, const char* text) {
+    code = c;
+    msg = text;
+  };
+  auto is_static = [](int rank, const int64_t* shape) {
+    for (int i = 0; i < rank; ++i)
+      if (shape[i] < 0) return false;
+    return true;
+  };
+  if (!a_shape || !b_shape || !c_shape) {
+    fail(FRISK_B200_E_GEMM_SHAPE, "legacy-gemm-shape: A, B, and C must be memrefs");
+  } else if (a_rank != 2 || b_rank != 2 || c_rank != 2) {
+    fail(FRISK_B200_E_GEMM_SHAPE, "legacy-gemm-shape: A, B, and C must have rank 2");
+  } else if (!is_static(2, a_shape) || !is_static(2, b_shape) || !is_static(2, c_shape)) {
+    fail(FRISK_B200_E_GEMM_SHAPE, "legacy-gemm-shape: A, B, and C must have static shapes");
+  } else if (m <= 0 || n <= 0 || k <= 0) {
+    fail(FRISK_B200_E_GEMM_SHAPE, "legacy-gemm-shape: M, N, and K must be positive");
+  } else if (a_dtype != b_dtype) {
+    fail(FRISK_B200_E_GEMM_TYPE, "legacy-gemm-type: A and B must have the same element type");
+  } else if (!(c_dtype == a_dtype ||
+               ((a_dtype == FRISK_B200_F16 || a_dtype == FRISK_B200_BF16) && c_dtype == FRISK_B200_F32))) {
+    fail(FRISK_B200_E_GEMM_TYPE, "legacy-gemm-type: C must match A/B or be f32 for f16/bf16 inputs");
+  } else {
+    int64_t am = a_shape[trans_a ? 1 : 0], ak = a_shape[trans_a ? 0 : 1];
+    int64_t bk = b_shape[trans_b ? 1 : 0], bn = b_shape[trans_b ? 0 : 1];
+    if (am != m || ak != k || bk != k || bn != n)
+      fail(FRISK_B200_E_GEMM_SHAPE, "legacy-gemm-shape: effective A/B shapes must match M/N/K");
+    else if (c_shape[0] != m || c_shape[1] != n)
+      fail(FRISK_B200_E_GEMM_SHAPE, "legacy-gemm-shape: C shape must be MxN");
+  }
+  if (message) *message = msg;
+  return code;
+}
+
+int frisk_b200_gemm_select(const frisk_b200_gemm_desc* d) {
+  int rc = frisk_b200_gemm_validate(d);
+  if (rc) return rc;
+  if (d->algo != FRISK_B200_ALGO_AUTO) {
+    if (d->algo == FRISK_B200_ALGO_SIMT_F32) return d->dtype_ab == FRISK_B200_F32 ? d->algo : FRISK_B200_E_UNSUPPORTED;
+    if (d->algo == FRISK_B200_ALGO_SKINNY) return skinny_supported(*d) ? d->algo : FRISK_B200_E_UNSUPPORTED;
+    if (d->algo == FRISK_B200_ALGO_TCGEN05) return tcgen05_supported(*d) ? d->algo : FRISK_B200_E_UNSUPPORTED;
+  }
+  if (d->dtype_ab == FRISK_B200_F32) return FRISK_B200_ALGO_SIMT_F32;
+  if (skinny_supported(*d)) return FRISK_B200_ALGO_SKINNY;
+  if (tcgen05_supported(*d)) return FRISK_B200_ALGO_TCGEN05;
+  return FRISK_B200_E_ALIGN;  // 16-bit operands whose pitch is not a multiple of 16 bytes
+}
+
+size_t frisk_b200_gemm_workspace_bytes(const frisk_b200_gemm_desc* d) {
+  int algo = frisk_b200_gemm_select(d);
+  if (algo == FRISK_B200_ALGO_SKINNY) return skinny_workspace_bytes(*d);
+  return 0;
+}
+
+int frisk_b200_gemm(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc* d, const void* A, const void* B, void* C,
+                    void* workspace, size_t workspace_bytes, void* stream) {
+  if (!ctx || !d || !A || !B || !C) return FRISK_B200_E_ARG;
+  int algo = frisk_b200_gemm_select(d);
+  if (algo < 0) return algo;
+  GemmExtents e = gemm_extents(*d);
+  if (ranges_overlap(C, e.c, A, e.a) || ranges_overlap(C, e.c, B, e.b)) return FRISK_B200_E_OVERLAP;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  FB_CUDA(ctx, cudaSetDevice(ctx->device));
+  switch (algo) {
+    case FRISK_B200_ALGO_SIMT_F32:
+      return launch_gemm_simt_f32(ctx, *d, static_cast<const float*>(A), static_cast<const float*>(B),
+                                  static_cast<float*>(C), s);
+    case FRISK_B200_ALGO_SKINNY: {
+      size_t need = skinny_workspace_bytes(*d);
+      if (!workspace) {
+        // library-owned scratch: zeroed when (re)allocated, left clean by every launch
+        std::lock_guard<std::mutex> lock(ctx->mu);
+        int rc = ensure_stage(ctx, 3, need, true);
+        if (rc) return rc;
+        workspace = ctx->stage[3].ptr;
+        workspace_bytes = ctx->stage[3].bytes;
+      }
+      return launch_gemm_skinny(ctx, *d, A, B, C, workspace, workspace_bytes, s);
+    }
+    case FRISK_B200_ALGO_TCGEN05:
+      return launch_gemm_tcgen05(ctx, *d, A, B, C, s);
+  }
+  return FRISK_B200_E_UNSUPPORTED;
+}
+
+int frisk_b200_gemm_host(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc* d, const void* A, const void* B,
+                         void* C) {
+  if (!ctx || !d || !A || !B || !C) return FRISK_B200_E_ARG;
+  int algo = frisk_b200_gemm_select(d);
+  if (algo < 0) return algo;
+  FB_CUDA(ctx, cudaSetDevice(ctx->device));
+  GemmExtents e = gemm_extents(*d);
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  int rc;
+  if ((rc = ensure_stage(ctx, 0, e.a, false))) return rc;
+  if ((rc = ensure_stage(ctx, 1, e.b, false))) return rc;
+  if ((rc = ensure_stage(ctx, 2, e.c, false))) return rc;
+  size_t need = frisk_b200_gemm_workspace_bytes(d);
+  if (need && (rc = ensure_stage(ctx, 3, need, true))) return rc;
+  cudaStream_t s = ctx->host_stream, s2 = ctx->copy_stream;
+  // A and B travel on two streams so that both copy engines are used
+  FB_CUDA(ctx, cudaMemcpyAsync(ctx->stage[0].ptr, A, e.a, cudaMemcpyHostToDevice, s));
+  FB_CUDA(ctx, cudaMemcpyAsync(ctx->stage[1].ptr, B, e.b, cudaMemcpyHostToDevice, s2));
+  if (!d->clear_accum) FB_CUDA(ctx, cudaMemcpyAsync(ctx->stage[2].ptr, C, e.c, cudaMemcpyHostToDevice, s2));
+  FB_CUDA(ctx, cudaEventRecord(ctx->ev[0], s2));
+  FB_CUDA(ctx, cudaStreamWaitEvent(s, ctx->ev[0], 0));
+  switch (algo) {
+    case FRISK_B200_ALGO_SIMT_F32:
+      rc = launch_gemm_simt_f32(ctx, *d, static_cast<const float*>(ctx->stage[0].ptr),
+                                static_cast<const float*>(ctx->stage[1].ptr), static_cast<float*>(ctx->stage[2].ptr), s);
+      break;
+    case FRISK_B200_ALGO_SKINNY:
+      rc = launch_gemm_skinny(ctx, *d, ctx->stage[0].ptr, ctx->stage[1].ptr, ctx->stage[2].ptr, ctx->stage[3].ptr,
+                              ctx->stage[3].bytes, s);
+      break;
+    default:
+      rc = launch_gemm_tcgen05(ctx, *d, ctx->stage[0].ptr, ctx->stage[1].ptr, ctx->stage[2].ptr, s);
+  }
+  if (rc) return rc;
+  FB_CUDA(ctx, cudaMemcpyAsync(C, ctx->stage[2].ptr, e.c, cudaMemcpyDeviceToHost, s));
+  FB_CUDA(ctx, cudaMemcpyAsync(ctx->h_status, ctx->d_status, sizeof(unsigned), cudaMemcpyDeviceToHost, s));
+  FB_CUDA(ctx, cudaStreamSynchronize(s));
+  ctx->last_status = (int)ctx->h_status[0];
+  if (ctx->last_status) {
+    cudaMemsetAsync(ctx->d_status, 0, sizeof(unsigned), s);
+    cudaStreamSynchronize(s);
+    return FRISK_B200_E_DEVICE_TIMEOUT;
+  }
+  return 0;
+}
+
+// ------------------------------------------------------------------------------ attention
+int frisk_b200_attention_validate(const frisk_b200_attn_desc* d) {
+  if (!d) return FRISK_B200_E_ARG;
+  if (d->B <= 0 || d->H <= 0 || d->S_q <= 0 || d->S_kv <= 0) return FRISK_B200_E_ATTN_SHAPE;
+  if (d->D != 64 && d->D != 128) return FRISK_B200_E_ATTN_SHAPE;
+  if (d->dtype_in != FRISK_B200_F16 && d->dtype_in != FRISK_B200_BF16) return FRISK_B200_E_UNSUPPORTED;
+  if (d->dtype_out != d->dtype_in && d->dtype_out != FRISK_B200_F32) return FRISK_B200_E_UNSUPPORTED;
+  if (d->causal && d->S_kv < d->S_q) return FRISK_B200_E_ATTN_SHAPE;
+  if ((int64_t)d->B * d->H > INT32_MAX) return FRISK_B200_E_ATTN_SHAPE;
+  if (!(d->scale == d->scale) || d->scale <= 0.f) return FRISK_B200_E_ARG;
+  return 0;
+}
+
+size_t frisk_b200_attention_workspace_bytes(const frisk_b200_attn_desc* d) {
+  (void)d;
+  return 0;  // the 5th "scratch" argument of the reference ABI is unused there as well
+}
+
+int frisk_b200_attention_fwd(frisk_b200_ctx* ctx, const frisk_b200_attn_desc* d, const void* Q, const void* K,
+                             const void* V, void* O, void* workspace, size_t workspace_bytes, void* stream) {
+  (void)workspace;
+  (void)workspace_bytes;
+  if (!ctx || !d || !Q || !K || !V || !O) return FRISK_B200_E_ARG;
+  int rc = frisk_b200_attention_validate(d);
+  if (rc) return rc;
+  size_t es = dtype_size(d->dtype_in), os = dtype_size(d->dtype_out);
+  size_t qb = (size_t)d->B * d->H * d->S_q * d->D * es, kb = (size_t)d->B * d->H * d->S_kv * d->D * es;
+  size_t ob = (size_t)d->B * d->H * d->S_q * d->D * os;
+  if (ranges_overlap(O, ob, Q, qb) || ranges_overlap(O, ob, K, kb) || ranges_overlap(O, ob, V, kb))
+    return FRISK_B200_E_OVERLAP;
+  for (const void* p : {Q, K, V, (const void*)O})
+    if (reinterpret_cast<uintptr_t>(p) & 15u) return FRISK_B200_E_ALIGN;
+  FB_CUDA(ctx, cudaSetDevice(ctx->device));
+  return launch_attention_fwd(ctx, *d, Q, K, V, O, static_cast<cudaStream_t>(stream));
+}
+
+int frisk_b200_attention_fwd_host(frisk_b200_ctx* ctx, const frisk_b200_attn_desc* d, const void* Q,
+                                  const void* K, const void* V, void* O) {
+  if (!ctx || !d || !Q || !K || !V || !O) return FRISK_B200_E_ARG;
+  int rc = frisk_b200_attention_validate(d);
+  if (rc) return rc;
+  FB_CUDA(ctx, cudaSetDevice(ctx->device));
+  size_t es = dtype_size(d->dtype_in), os = dtype_size(d->dtype_out);
+  size_t qb = (size_t)d->B * d->H * d->S_q * d->D * es, kb = (size_t)d->B * d->H * d->S_kv * d->D * es;
+  size_t ob = (size_t)d->B * d->H * d->S_q * d->D * os;
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  if ((rc = ensure_stage(ctx, 0, qb, false))) return rc;
+  if ((rc = ensure_stage(ctx, 1, kb, false))) return rc;
+  if ((rc = ensure_stage(ctx, 2, ob, false))) return rc;
+  if ((rc = ensure_stage(ctx, 4, kb, false))) return rc;
+  cudaStream_t s = ctx->host_stream, s2 = ctx->copy_stream;
+  FB_CUDA(ctx, cudaMemcpyAsync(ctx->stage[0].ptr, Q, qb, cudaMemcpyHostToDevice, s));
+  FB_CUDA(ctx, cudaMemcpyAsync(ctx->stage[1].ptr, K, kb, cudaMemcpyHostToDevice, s2));
+  FB_CUDA(ctx, cudaMemcpyAsync(ctx->stage[4].ptr, V, kb, cudaMemcpyHostToDevice, s));
+  FB_CUDA(ctx, cudaEventRecord(ctx->ev[0], s2));
+  FB_CUDA(ctx, cudaStreamWaitEvent(s, ctx->ev[0], 0));
+  rc = launch_attention_fwd(ctx, *d, ctx->stage[0].ptr, ctx->stage[1].ptr, ctx->stage[4].ptr, ctx->stage[2].ptr, s);
+  if (rc) return rc;
+  FB_CUDA(ctx, cudaMemcpyAsync(O, ctx->stage[2].ptr, ob, cudaMemcpyDeviceToHost, s));
+  FB_CUDA(ctx, cudaMemcpyAsync(ctx->h_status, ctx->d_status, sizeof(unsigned), cudaMemcpyDeviceToHost, s));
+  FB_CUDA(ctx, cudaStreamSynchronize(s));
+  ctx->last_status = (int)ctx->h_status[0];
+  if (ctx->last_status) {
+    cudaMemsetAsync(ctx->d_status, 0, sizeof(unsigned), s);
+    cudaStreamSynchronize(s);
+    return FRISK_B200_E_DEVICE_TIMEOUT;
+  }
+  return 0;
+}
+
+int frisk_b200_convert_f32(frisk_b200_ctx* ctx, const float* src, void* dst, int64_t count, int32_t dtype_dst,
+                           void* stream) {
+  if (!ctx || !src || !dst || count < 0) return FRISK_B200_E_ARG;
+  FB_CUDA(ctx, cudaSetDevice(ctx->device));
+  return launch_convert_f32(src, dst, count, dtype_dst, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

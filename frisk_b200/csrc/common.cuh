@@ -1,0 +1,95 @@
+// Shared host-side declarations of libfrisk_b200: the context, error helpers and the
+// per-kernel launch functions that api.cu dispatches to.
+#pragma once
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#include <map>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "../../include/frisk_b200.h"
+
+namespace fb {
+
+constexpr int kNumSMsDefault = 148;
+
+struct StagingBuffer {
+  void* ptr = nullptr;
+  size_t bytes = 0;
+};
+
+}  // namespace fb
+
+struct frisk_b200_ctx {
+  int device = 0;
+  int num_sms = fb::kNumSMsDefault;
+  int last_cuda = 0;
+  int last_status = 0;
+  unsigned* d_status = nullptr;  // device status word (first failing wait records its code)
+  unsigned* h_status = nullptr;  // pinned mirror
+  // staging for the *_host entry points and library-owned workspace
+  fb::StagingBuffer stage[5];
+  cudaStream_t host_stream = nullptr;
+  cudaStream_t copy_stream = nullptr;
+  cudaEvent_t ev[8] = {};
+  std::mutex mu;
+};
+
+namespace fb {
+
+inline size_t dtype_size(int dt) { return dt == FRISK_B200_F32 ? 4 : 2; }
+inline bool dtype_ok(int dt) { return dt == FRISK_B200_F32 || dt == FRISK_B200_F16 || dt == FRISK_B200_BF16; }
+
+#define FB_CUDA(ctx, expr)                          \
+  do {                                              \
+    cudaError_t e__ = (expr);                       \
+    if (e__ != cudaSuccess) {                       \
+      if (ctx) (ctx)->last_cuda = (int)e__;         \
+      return FRISK_B200_E_CUDA;                     \
+    }                                               \
+  } while (0)
+
+// resolved leading dimensions (elements)
+struct GemmDims {
+  int64_t M, N, K, lda, ldb, ldc;
+};
+inline GemmDims resolve_dims(const frisk_b200_gemm_desc& d) {
+  GemmDims g{d.M, d.N, d.K, d.lda, d.ldb, d.ldc};
+  if (g.lda == 0) g.lda = d.trans_a ? d.M : d.K;
+  if (g.ldb == 0) g.ldb = d.trans_b ? d.K : d.N;
+  if (g.ldc == 0) g.ldc = d.N;
+  return g;
+}
+
+// ---- kernel launchers (one per .cu file) --------------------------------------------
+int launch_gemm_simt_f32(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc& d, const float* A, const float* B,
+                         float* C, cudaStream_t s);
+
+size_t skinny_workspace_bytes(const frisk_b200_gemm_desc& d);
+bool skinny_supported(const frisk_b200_gemm_desc& d);
+int launch_gemm_skinny(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc& d, const void* A, const void* B, void* C,
+                       void* ws, size_t ws_bytes, cudaStream_t s);
+
+bool tcgen05_supported(const frisk_b200_gemm_desc& d);
+int launch_gemm_tcgen05(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc& d, const void* A, const void* B,
+                        void* C, cudaStream_t s);
+
+int launch_attention_fwd(frisk_b200_ctx* ctx, const frisk_b200_attn_desc& d, const void* Q, const void* K,
+                         const void* V, void* O, cudaStream_t s);
+
+int launch_convert_f32(const float* src, void* dst, int64_t n, int dtype, cudaStream_t s);
+
+// TMA descriptor encode through the driver entry point (no link-time libcuda dependency)
+int encode_tmap_2d(CUtensorMap* out, int dtype, const void* base, uint64_t inner, uint64_t outer,
+                   uint64_t outer_stride_bytes, uint32_t box_inner, uint32_t box_outer, bool swizzle128);
+int encode_tmap_3d(CUtensorMap* out, int dtype, const void* base, uint64_t d0, uint64_t d1, uint64_t d2,
+                   uint64_t stride1_bytes, uint64_t stride2_bytes, uint32_t b0, uint32_t b1, uint32_t b2,
+                   bool swizzle128);
+
+}  // namespace fb

@@ -1,0 +1,281 @@
+// Decode-shape ("skinny") GEMM: Y[M<=16, N] = X[M, K] . W[N, K]^T for fp16/bf16, fp32
+// accumulation.  Contract: `frisk.gemm` with trans_a=0, trans_b=1
+// (lib/Dialect/Frisk/IR/FriskOps.cpp:406-426).  The weight matrix is read exactly once, so
+// the kernel is bound by HBM bandwidth; everything is arranged around keeping many 16-byte
+// weight loads in flight.
+//
+// * K is split across CTAs (split s = blockIdx.x % S): a CTA stages only its K-slice of X
+//   in shared memory (16 x K/S elements, rows padded by 64 bytes so that the fragment
+//   reads below are bank-conflict free).
+// * A warp owns one group of 8 weight rows at a time, taken from a per-split queue in the
+//   workspace (an atomic counter), so all warps stay busy to the end of the stream.
+// * Each lane loads 16 bytes (8 consecutive k) of "its" weight row.  Because a dot product
+//   does not care about the order of k, those 8 values feed two m16n8k16 tensor-core MMAs
+//   directly as B fragments, with the matching 8 values of X rows g and g+8 as A
+//   fragments: no shuffles, no shared-memory staging of W.
+// * With S > 1 a warp writes its fp32 16x8 partial to the workspace, takes a ticket for the
+//   row group, and the warp that draws the last ticket adds the S partials in split order
+//   (deterministic) and writes the rounded output.
+// All control words are left at zero when the kernel ends.
+#include "common.cuh"
+
+namespace fb {
+namespace {
+
+constexpr int kThreads = 512;
+constexpr int kWarps = kThreads / 32;
+constexpr int kUnroll = 8;               // 16-byte weight loads in flight per lane
+constexpr int kStepK = 32;               // k covered by one warp step (4 lanes x 8 elements)
+constexpr int kChunkK = kStepK * kUnroll;  // 256
+constexpr int kRowPadBytes = 64;
+constexpr int kCtlInts = 64;             // ctr[0..31], done = [32]
+constexpr int kMaxSplit = 32;
+constexpr size_t kMaxSmem = 200 * 1024;
+
+struct SkinnyPlan {
+  int S;            // K splits
+  int kslice;       // elements per split (multiple of kChunkK)
+  int ngroups;      // ceil(N / 8)
+  size_t smem;      // dynamic shared bytes
+  size_t off_tickets, off_partials, ws_bytes;
+  int grid;
+};
+
+__device__ __forceinline__ uint4 ldg_stream(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+
+template <typename T>
+__device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1);
+template <>
+__device__ __forceinline__ void mma16816<__half>(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                                 uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+      "{%0, %1, %2, %3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+template <>
+__device__ __forceinline__ void mma16816<__nv_bfloat16>(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                                        uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+      "{%0, %1, %2, %3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <typename T>
+__device__ __forceinline__ float to_f32(T v);
+template <>
+__device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(v); }
+template <>
+__device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <typename T>
+__device__ __forceinline__ T from_f32(float v);
+template <>
+__device__ __forceinline__ __half from_f32<__half>(float v) { return __float2half_rn(v); }
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+template <>
+__device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float to_f32<float>(float v) { return v; }
+
+// TO = output element type (T or float)
+template <typename T, typename TO>
+__global__ void __launch_bounds__(kThreads, 1)
+    gemm_skinny_kernel(const T* __restrict__ X, const T* __restrict__ W, TO* __restrict__ Y, int M, int N,
+                       int K, int64_t ldx, int64_t ldw, int64_t ldy, int S, int kslice, int ngroups,
+                       int accumulate, unsigned* __restrict__ ctl, unsigned* __restrict__ tickets,
+                       float* __restrict__ partials) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int tid = threadIdx.x, lane = tid & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int s = blockIdx.x % S;
+  const int kbeg = s * kslice;
+  const int klen = max(0, min(K, kbeg + kslice) - kbeg);  // valid k in this slice (multiple of 8)
+  const int pitch = kslice * (int)sizeof(T) + kRowPadBytes;
+
+  // ---- stage this split's slice of X (rows >= M and k beyond the slice are zero)
+  {
+    const int vec_per_row = kslice / 8;
+    for (int i = tid; i < 16 * vec_per_row; i += kThreads) {
+      int r = i / vec_per_row, kv = (i % vec_per_row) * 8;
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (r < M && kv < klen) v = __ldg(reinterpret_cast<const uint4*>(X + (int64_t)r * ldx + kbeg + kv));
+      *reinterpret_cast<uint4*>(smem_raw + (size_t)r * pitch + (size_t)kv * sizeof(T)) = v;
+    }
+  }
+  __syncthreads();
+
+  const unsigned char* xs_lo = smem_raw + (size_t)g * pitch + (size_t)t * 8 * sizeof(T);
+  const unsigned char* xs_hi = xs_lo + (size_t)8 * pitch;
+  const int Npad = ngroups * 8;
+
+  while (true) {
+    unsigned ng = 0;
+    if (lane == 0) ng = atomicAdd(&ctl[s], 1u);
+    ng = __shfl_sync(0xffffffffu, ng, 0);
+    if (ng >= (unsigned)ngroups) break;
+
+    const int n_row = min((int)ng * 8 + g, N - 1);
+    const T* wrow = W + (int64_t)n_row * ldw + kbeg + t * 8;
+    float acc0[4] = {0.f, 0.f, 0.f, 0.f}, acc1[4] = {0.f, 0.f, 0.f, 0.f};
+
+    for (int k0 = 0; k0 < klen; k0 += kChunkK) {
+      uint4 w[kUnroll];
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        int kk = k0 + u * kStepK + t * 8;
+        w[u] = (kk < klen) ? ldg_stream(wrow + k0 + u * kStepK) : make_uint4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        size_t off = (size_t)(k0 + u * kStepK) * sizeof(T);
+        uint4 xa = *reinterpret_cast<const uint4*>(xs_lo + off);
+        uint4 xb = *reinterpret_cast<const uint4*>(xs_hi + off);
+        mma16816<T>(acc0, xa.x, xb.x, xa.y, xb.y, w[u].x, w[u].y);
+        mma16816<T>(acc1, xa.z, xb.z, xa.w, xb.w, w[u].z, w[u].w);
+      }
+    }
+    float c[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) c[i] = acc0[i] + acc1[i];
+
+    const int col = (int)ng * 8 + 2 * t;  // output columns col, col+1 ; rows g and g+8
+    if (S > 1) {
+      float* p = partials + ((size_t)s * 16 + g) * Npad + col;
+      __stcg(reinterpret_cast<float2*>(p), make_float2(c[0], c[1]));
+      __stcg(reinterpret_cast<float2*>(p + (size_t)8 * Npad), make_float2(c[2], c[3]));
+      __threadfence();
+      __syncwarp();
+      unsigned ticket = 0;
+      if (lane == 0) ticket = atomicAdd(&tickets[ng], 1u);
+      ticket = __shfl_sync(0xffffffffu, ticket, 0);
+      if (ticket != (unsigned)(S - 1)) continue;
+      __threadfence();
+      c[0] = c[1] = c[2] = c[3] = 0.f;
+      for (int ss = 0; ss < S; ++ss) {
+        const float* q = partials + ((size_t)ss * 16 + g) * Npad + col;
+        float2 lo = __ldcg(reinterpret_cast<const float2*>(q));
+        float2 hi = __ldcg(reinterpret_cast<const float2*>(q + (size_t)8 * Npad));
+        c[0] += lo.x; c[1] += lo.y; c[2] += hi.x; c[3] += hi.y;
+      }
+      if (lane == 0) tickets[ng] = 0;
+    }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      int r = g + 8 * h;
+      if (r >= M) continue;
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        int cc = col + j;
+        if (cc >= N) continue;
+        TO* y = Y + (int64_t)r * ldy + cc;
+        float v = c[2 * h + j];
+        if (accumulate) v += to_f32<TO>(*y);
+        *y = from_f32<TO>(v);
+      }
+    }
+  }
+
+  // ---- leave the queue counters at zero for the next launch
+  __syncthreads();
+  if (tid == 0) {
+    __threadfence();
+    unsigned d = atomicAdd(&ctl[32], 1u);
+    if (d == gridDim.x - 1) {
+      for (int i = 0; i < S; ++i) ctl[i] = 0;
+      ctl[32] = 0;
+      __threadfence();
+    }
+  }
+}
+
+SkinnyPlan make_plan(const frisk_b200_gemm_desc& d, int num_sms) {
+  SkinnyPlan p{};
+  size_t es = dtype_size(d.dtype_ab);
+  p.ngroups = (int)((d.N + 7) / 8);
+  int S = 1;
+  auto slice_of = [&](int s) { return (int)(((d.K + s - 1) / s + kChunkK - 1) / kChunkK * kChunkK); };
+  auto smem_of = [&](int s) { return (size_t)16 * ((size_t)slice_of(s) * es + kRowPadBytes); };
+  while (S < kMaxSplit && smem_of(S) > kMaxSmem) ++S;
+  // enough warp-sized work items to keep every warp of the machine busy a few times over
+  long want_items = (long)num_sms * kWarps * 4;
+  while (S < kMaxSplit && (long)p.ngroups * S < want_items && slice_of(S + 1) >= 2 * kChunkK &&
+         slice_of(S + 1) < slice_of(S))
+    ++S;
+  if (const char* e = getenv("FRISK_B200_SKINNY_SPLIT")) {
+    int v = atoi(e);
+    if (v >= 1 && v <= kMaxSplit && smem_of(v) <= kMaxSmem) S = v;
+  }
+  p.S = S;
+  p.kslice = slice_of(S);
+  p.smem = smem_of(S);
+  p.grid = (num_sms / S) * S;
+  if (p.grid < S) p.grid = S;
+  p.off_tickets = kCtlInts * sizeof(unsigned);
+  size_t tick_bytes = ((size_t)p.ngroups * sizeof(unsigned) + 255) / 256 * 256;
+  p.off_partials = p.off_tickets + tick_bytes;
+  p.ws_bytes = p.off_partials + (S > 1 ? (size_t)S * 16 * p.ngroups * 8 * sizeof(float) : 0);
+  return p;
+}
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+template <typename T, typename TO>
+int launch_typed(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc& d, const SkinnyPlan& p, const void* A,
+                 const void* B, void* C, void* ws, cudaStream_t s) {
+  GemmDims g = resolve_dims(d);
+  auto kern = gemm_skinny_kernel<T, TO>;
+  FB_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p.smem));
+  unsigned char* w = static_cast<unsigned char*>(ws);
+  kern<<<p.grid, kThreads, p.smem, s>>>(static_cast<const T*>(A), static_cast<const T*>(B), static_cast<TO*>(C),
+                                        (int)g.M, (int)g.N, (int)g.K, g.lda, g.ldb, g.ldc, p.S, p.kslice,
+                                        p.ngroups, d.clear_accum ? 0 : 1, reinterpret_cast<unsigned*>(w),
+                                        reinterpret_cast<unsigned*>(w + p.off_tickets),
+                                        reinterpret_cast<float*>(w + p.off_partials));
+  FB_CUDA(ctx, cudaGetLastError());
+  return 0;
+}
+
+}  // namespace
+
+bool skinny_supported(const frisk_b200_gemm_desc& d) {
+  if (d.dtype_ab != FRISK_B200_F16 && d.dtype_ab != FRISK_B200_BF16) return false;
+  if (d.trans_a || !d.trans_b) return false;
+  if (d.M < 1 || d.M > 16) return false;
+  GemmDims g = resolve_dims(d);
+  if (g.K % 8 || g.lda % 8 || g.ldb % 8) return false;
+  if (g.N > (int64_t)INT32_MAX / 16 || g.K > INT32_MAX / 2) return false;
+  return true;
+}
+
+size_t skinny_workspace_bytes(const frisk_b200_gemm_desc& d) {
+  return make_plan(d, kNumSMsDefault).ws_bytes;
+}
+
+// Also used by the fixed-capacity entry point, which passes its own scratch.
+int launch_gemm_skinny(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc& d, const void* A, const void* B, void* C,
+                       void* ws, size_t ws_bytes, cudaStream_t s) {
+  if (!skinny_supported(d)) return FRISK_B200_E_UNSUPPORTED;
+  if (!aligned16(A) || !aligned16(B)) return FRISK_B200_E_ALIGN;
+  SkinnyPlan p = make_plan(d, kNumSMsDefault);
+  if (!ws || ws_bytes < p.ws_bytes) return FRISK_B200_E_WORKSPACE;
+  if (!aligned16(ws)) return FRISK_B200_E_ALIGN;
+  bool out32 = d.dtype_c == FRISK_B200_F32;
+  if (d.dtype_ab == FRISK_B200_F16)
+    return out32 ? launch_typed<__half, float>(ctx, d, p, A, B, C, ws, s)
+                 : launch_typed<__half, __half>(ctx, d, p, A, B, C, ws, s);
+  return out32 ? launch_typed<__nv_bfloat16, float>(ctx, d, p, A, B, C, ws, s)
+               : launch_typed<__nv_bfloat16, __nv_bfloat16>(ctx, d, p, A, B, C, ws, s);
+}
+
+}  // namespace fb

@@ -1,0 +1,382 @@
+// fp16 / bf16 GEMM on the 5th-generation tensor cores (tcgen05), fp32 accumulation in
+// tensor memory.  Contract: `frisk.gemm` with f16/bf16 operands and a C of the same type or
+// f32 (lib/Dialect/Frisk/IR/FriskOps.cpp:406-426,
+// lib/Dialect/Frisk/IR/LegacyImportSemantics.cpp:26-44).
+//
+// One persistent CTA per SM, 6 warps with fixed roles:
+//   warp 0    TMA producer: A and B tiles -> 4-stage shared-memory ring (full/empty mbarriers)
+//   warp 1    MMA issuer:   one thread issues tcgen05.mma (128 x BN x 16) per k16 slice,
+//                           tcgen05.commit releases the stage / publishes the accumulator
+//   warps 2-5 epilogue:     tcgen05.ld of the finished accumulator, conversion, global stores
+// Two accumulators (2 x BN TMEM columns) let the epilogue of tile i overlap the main loop of
+// tile i+1.
+//
+// Shared-memory operand images are the canonical 128-byte-swizzle layouts (rows of 64
+// 16-bit elements, 1024-byte aligned stages): K-major for an operand that is contiguous
+// along K in global memory, MN-major otherwise.  These are the images Frisk's layout
+// inference proposes for 16-bit MMA operands
+// (lib/Dialect/Frisk/Target/SM90/SM90GemmConstraints.cpp:121-138); TMA writes them directly.
+// No TMA load uses cluster multicast.
+#include "common.cuh"
+#include "ptx.cuh"
+
+namespace fb {
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 64;       // one 128-byte swizzle span of 16-bit elements
+constexpr int UMMA_K = 16;
+constexpr int kStages = 4;
+constexpr int kThreads = 192;
+constexpr int kEpiWarp0 = 2;
+constexpr int kGroupM = 8;   // tile raster: columns of 8 M-tiles, for L2 reuse of B
+
+template <int BN>
+struct SmemLayout {
+  static constexpr int kABytes = BM * BK * 2;
+  static constexpr int kBBytes = BN * BK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kBarOffset = kStages * kStageBytes;
+  static constexpr int kTotal = kBarOffset + 256 + 1024;  // barriers + alignment slack
+};
+
+struct TileCoord {
+  int m, n;
+};
+__device__ __forceinline__ TileCoord tile_coord(int t, int tiles_m, int tiles_n) {
+  int per_group = kGroupM * tiles_n;
+  int group = t / per_group;
+  int first_m = group * kGroupM;
+  int gsize = min(tiles_m - first_m, kGroupM);
+  int r = t - group * per_group;
+  return TileCoord{first_m + r % gsize, r / gsize};
+}
+
+template <typename TO>
+__device__ __forceinline__ void store_row_chunk(TO* p, const uint32_t (&v)[32], int valid, bool vec_ok,
+                                                bool accumulate);
+
+template <>
+__device__ __forceinline__ void store_row_chunk<float>(float* p, const uint32_t (&v)[32], int valid, bool vec_ok,
+                                                       bool accumulate) {
+  if (vec_ok && valid == 32) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      float4 o = make_float4(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]),
+                             __uint_as_float(v[4 * i + 2]), __uint_as_float(v[4 * i + 3]));
+      if (accumulate) {
+        float4 c = *reinterpret_cast<const float4*>(p + 4 * i);
+        o.x += c.x; o.y += c.y; o.z += c.z; o.w += c.w;
+      }
+      *reinterpret_cast<float4*>(p + 4 * i) = o;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 32; ++i)
+      if (i < valid) p[i] = accumulate ? p[i] + __uint_as_float(v[i]) : __uint_as_float(v[i]);
+  }
+}
+
+template <typename T2, typename T>
+__device__ __forceinline__ uint32_t pack2(float a, float b);
+template <>
+__device__ __forceinline__ uint32_t pack2<__half2, __half>(float a, float b) {
+  __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+template <>
+__device__ __forceinline__ uint32_t pack2<__nv_bfloat162, __nv_bfloat16>(float a, float b) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+__device__ __forceinline__ float2 unpack2(uint32_t u, __half) {
+  return __half22float2(*reinterpret_cast<__half2*>(&u));
+}
+__device__ __forceinline__ float2 unpack2(uint32_t u, __nv_bfloat16) {
+  return __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&u));
+}
+
+template <typename T, typename T2>
+__device__ __forceinline__ void store_row_chunk16(T* p, const uint32_t (&v)[32], int valid, bool vec_ok,
+                                                  bool accumulate) {
+  if (vec_ok && valid == 32) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float f[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(v[8 * i + j]);
+      if (accumulate) {
+        uint4 c = *reinterpret_cast<const uint4*>(p + 8 * i);
+        float2 c0 = unpack2(c.x, T()), c1 = unpack2(c.y, T()), c2 = unpack2(c.z, T()), c3 = unpack2(c.w, T());
+        f[0] += c0.x; f[1] += c0.y; f[2] += c1.x; f[3] += c1.y;
+        f[4] += c2.x; f[5] += c2.y; f[6] += c3.x; f[7] += c3.y;
+      }
+      uint4 o;
+      o.x = pack2<T2, T>(f[0], f[1]);
+      o.y = pack2<T2, T>(f[2], f[3]);
+      o.z = pack2<T2, T>(f[4], f[5]);
+      o.w = pack2<T2, T>(f[6], f[7]);
+      *reinterpret_cast<uint4*>(p + 8 * i) = o;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      if (i < valid) {
+        float f = __uint_as_float(v[i]);
+        if (accumulate) f += static_cast<float>(p[i]);
+        p[i] = static_cast<T>(f);
+      }
+    }
+  }
+}
+template <>
+__device__ __forceinline__ void store_row_chunk<__half>(__half* p, const uint32_t (&v)[32], int valid,
+                                                        bool vec_ok, bool accumulate) {
+  store_row_chunk16<__half, __half2>(p, v, valid, vec_ok, accumulate);
+}
+template <>
+__device__ __forceinline__ void store_row_chunk<__nv_bfloat16>(__nv_bfloat16* p, const uint32_t (&v)[32],
+                                                               int valid, bool vec_ok, bool accumulate) {
+  store_row_chunk16<__nv_bfloat16, __nv_bfloat162>(p, v, valid, vec_ok, accumulate);
+}
+
+// A_MN / B_MN: the operand is contiguous along M / N in global memory (MN-major image).
+template <typename TO, int BN, bool BF16, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(kThreads, 1)
+    gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                        TO* __restrict__ C, int M, int N, int K, int64_t ldc, int accumulate, int vec_c,
+                        unsigned* __restrict__ status) {
+  using L = SmemLayout<BN>;
+  extern __shared__ unsigned char smem_unaligned[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>(
+      (reinterpret_cast<uintptr_t>(smem_unaligned) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::kBarOffset);
+  uint64_t* empty_bar = full_bar + kStages;
+  uint64_t* acc_full = empty_bar + kStages;   // [2]
+  uint64_t* acc_empty = acc_full + 2;         // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
+  const int num_tiles = tiles_m * tiles_n;
+  const int num_kb = (K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kStages; ++i) {
+      mbar_init(&full_bar[i], 1);
+      mbar_init(&empty_bar[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&acc_full[i], 1);
+      mbar_init(&acc_empty[i], 4);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 2 * BN);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        TileCoord tc = tile_coord(t, tiles_m, tiles_n);
+        const int m0 = tc.m * BM, n0 = tc.n * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, status, ST_TIMEOUT_EMPTY)) {
+            ok = false;
+            break;
+          }
+          unsigned char* sa = smem + stage * L::kStageBytes;
+          unsigned char* sb = sa + L::kABytes;
+          mbar_expect_tx(&full_bar[stage], L::kStageBytes);
+          const int k0 = kb * BK;
+          if (A_MN) {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j)
+              tma_load_2d(sa + j * (BK * 128), &tmap_a, &full_bar[stage], m0 + j * 64, k0);
+          } else {
+            tma_load_2d(sa, &tmap_a, &full_bar[stage], k0, m0);
+          }
+          if (B_MN) {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)
+              tma_load_2d(sb + j * (BK * 128), &tmap_b, &full_bar[stage], n0 + j * 64, k0);
+          } else {
+            tma_load_2d(sb, &tmap_b, &full_bar[stage], k0, n0);
+          }
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_f16(BM, BN, BF16, A_MN, B_MN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag, status, ST_TIMEOUT_ACC_EMPTY)) break;
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, abort_flag, status, ST_TIMEOUT_FULL)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t sa = smem_u32(smem + stage * L::kStageBytes);
+          const uint32_t sb = sa + L::kABytes;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            uint64_t da = A_MN ? umma_desc_mnmajor_sw128(sa + k * (UMMA_K * 128), BK * 128, 1024)
+                               : umma_desc_kmajor_sw128(sa + k * (UMMA_K * 2));
+            uint64_t db = B_MN ? umma_desc_mnmajor_sw128(sb + k * (UMMA_K * 128), BK * 128, 1024)
+                               : umma_desc_kmajor_sw128(sb + k * (UMMA_K * 2));
+            umma_f16_ss(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[stage]);  // stage reusable once these MMAs have read it
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (!ok) break;
+        umma_commit(&acc_full[acc]);  // accumulator complete
+        if (++acc == 2) {
+          acc = 0;
+          acc_phase ^= 1;
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue
+    const int quad = warp & 3;  // TMEM lanes [32*quad, 32*quad+32) are this warp's
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+      TileCoord tc = tile_coord(t, tiles_m, tiles_n);
+      const int m0 = tc.m * BM, n0 = tc.n * BN;
+      if (!mbar_wait(&acc_full[acc], acc_phase, abort_flag, status, ST_TIMEOUT_ACC_FULL)) break;
+      tc_fence_after_sync();
+      const int row = m0 + quad * 32 + lane;
+      const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(quad * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(taddr + c * 32, v);
+        tmem_ld_wait();
+        const int col = n0 + c * 32;
+        if (row < M && col < N)
+          store_row_chunk<TO>(C + (int64_t)row * ldc + col, v, min(32, N - col), vec_c != 0, accumulate != 0);
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[acc]);
+      if (++acc == 2) {
+        acc = 0;
+        acc_phase ^= 1;
+      }
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  if (*abort_flag) {
+    // a wait ran out somewhere: give copies that are still in flight time to land
+    unsigned long long t0 = globaltimer();
+    while (globaltimer() - t0 < 200000ull) __nanosleep(1000);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 2 * BN);
+  }
+}
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+template <typename TO, int BN, bool BF16, bool A_MN, bool B_MN>
+int launch_cfg(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc& d, const void* A, const void* B, void* C,
+               cudaStream_t s) {
+  GemmDims g = resolve_dims(d);
+  CUtensorMap ta, tb;
+  int rc;
+  // A: K-major -> dims {K, M}, box {64, 128};  MN-major (stored [K,M]) -> dims {M, K}, box {64, 64}
+  if (A_MN)
+    rc = encode_tmap_2d(&ta, d.dtype_ab, A, (uint64_t)g.M, (uint64_t)g.K, (uint64_t)g.lda * 2, 64, BK, true);
+  else
+    rc = encode_tmap_2d(&ta, d.dtype_ab, A, (uint64_t)g.K, (uint64_t)g.M, (uint64_t)g.lda * 2, BK, BM, true);
+  if (rc) { if (ctx) ctx->last_cuda = rc; return FRISK_B200_E_CUDA; }
+  if (B_MN)
+    rc = encode_tmap_2d(&tb, d.dtype_ab, B, (uint64_t)g.N, (uint64_t)g.K, (uint64_t)g.ldb * 2, 64, BK, true);
+  else
+    rc = encode_tmap_2d(&tb, d.dtype_ab, B, (uint64_t)g.K, (uint64_t)g.N, (uint64_t)g.ldb * 2, BK, BN, true);
+  if (rc) { if (ctx) ctx->last_cuda = rc; return FRISK_B200_E_CUDA; }
+
+  auto kern = gemm_tcgen05_kernel<TO, BN, BF16, A_MN, B_MN>;
+  using L = SmemLayout<BN>;
+  FB_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
+  int tiles = (int)(((g.M + BM - 1) / BM) * ((g.N + BN - 1) / BN));
+  int grid = tiles < ctx->num_sms ? tiles : ctx->num_sms;
+  int vec_c = aligned16(C) && (g.ldc * sizeof(TO)) % 16 == 0;
+  kern<<<grid, kThreads, L::kTotal, s>>>(ta, tb, static_cast<TO*>(C), (int)g.M, (int)g.N, (int)g.K, g.ldc,
+                                         d.clear_accum ? 0 : 1, vec_c, ctx->d_status);
+  FB_CUDA(ctx, cudaGetLastError());
+  return 0;
+}
+
+template <typename TO, int BN, bool BF16>
+int launch_major(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc& d, const void* A, const void* B, void* C,
+                 cudaStream_t s) {
+  bool a_mn = d.trans_a != 0;   // A stored [K,M]
+  bool b_mn = d.trans_b == 0;   // B stored [K,N]
+  if (a_mn) {
+    if (b_mn) return launch_cfg<TO, BN, BF16, true, true>(ctx, d, A, B, C, s);
+    return launch_cfg<TO, BN, BF16, true, false>(ctx, d, A, B, C, s);
+  }
+  if (b_mn) return launch_cfg<TO, BN, BF16, false, true>(ctx, d, A, B, C, s);
+  return launch_cfg<TO, BN, BF16, false, false>(ctx, d, A, B, C, s);
+}
+
+}  // namespace
+
+bool tcgen05_supported(const frisk_b200_gemm_desc& d) {
+  if (d.dtype_ab != FRISK_B200_F16 && d.dtype_ab != FRISK_B200_BF16) return false;
+  GemmDims g = resolve_dims(d);
+  // TMA: 16-byte pitches; 32-bit coordinates
+  if (g.lda % 8 || g.ldb % 8) return false;
+  if (g.M > INT32_MAX || g.N > INT32_MAX || g.K > INT32_MAX) return false;
+  return true;
+}
+
+int launch_gemm_tcgen05(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc& d, const void* A, const void* B,
+                        void* C, cudaStream_t s) {
+  if (!tcgen05_supported(d)) return FRISK_B200_E_UNSUPPORTED;
+  if (!aligned16(A) || !aligned16(B)) return FRISK_B200_E_ALIGN;
+  const bool bf = d.dtype_ab == FRISK_B200_BF16;
+  if (d.dtype_c == FRISK_B200_F32)
+    return bf ? launch_major<float, 256, true>(ctx, d, A, B, C, s) : launch_major<float, 256, false>(ctx, d, A, B, C, s);
+  if (bf) return launch_major<__nv_bfloat16, 256, true>(ctx, d, A, B, C, s);
+  return launch_major<__half, 256, false>(ctx, d, A, B, C, s);
+}
+
+}  // namespace fb

@@ -1,0 +1,191 @@
+"""``execute``: the run entry the reference lacks.
+
+The reference's ``bind_test`` builds a GEMM through the builders and prints it
+(``test/python/bind_test.py:64-66``); its NVIDIA lowering reaches a GPU only through
+export -> PTX emission -> Triton -> ``cuLaunchKernel``
+(``benchmark/layout/execution/run_execution.py:23-31,84``).  Here the kernel op is
+pattern-matched on the host and dispatched through the C ABI of ``libfrisk_b200``:
+
+* a kernel whose only computation is one ``frisk.gemm`` over its global memref
+  arguments, possibly nested in ``frisk.parallel`` / ``frisk.block`` / ``frisk.for``
+  (tile shapes there are scheduling hints; the hand-written kernels fix their own);
+* the attention-forward graph, entered through :func:`attention_forward` with the
+  launch contract of ``tiled_attention.py:28-61`` (compact BHSD, spec dict B/H/N/D).
+
+Device memory, streams and process groups come from torch; the arithmetic does not.
+"""
+import math
+
+from . import capi, ir
+
+_TORCH_DTYPE = None
+
+
+def _torch():
+    import torch
+    global _TORCH_DTYPE
+    if _TORCH_DTYPE is None:
+        _TORCH_DTYPE = {torch.float32: capi.F32, torch.float16: capi.F16, torch.bfloat16: capi.BF16}
+    return torch
+
+
+_contexts = {}
+
+
+def context_for(device_index):
+    """One library context per device, created on first use."""
+    ctx = _contexts.get(device_index)
+    if ctx is None:
+        ctx = capi.Context(device_index)
+        _contexts[device_index] = ctx
+    return ctx
+
+
+def _stream_ptr(stream, device):
+    torch = _torch()
+    s = stream if stream is not None else torch.cuda.current_stream(device)
+    return s.cuda_stream if hasattr(s, "cuda_stream") else int(s)
+
+
+def _find_gemm(kernel):
+    """Return (gemm_op, enclosing_ops) or raise ValueError naming what is unsupported."""
+    found = []
+
+    def visit(op, chain):
+        for r in op.regions:
+            for b in r.blocks:
+                for child in b.operations:
+                    if isinstance(child, ir.GemmOp):
+                        found.append((child, chain))
+                    elif isinstance(child, (ir.ParallelOp, ir.BlockOp, ir.ForOp)):
+                        visit(child, chain + [child])
+                    elif isinstance(child, (ir.AllocBufferOp, ir.EndOp)):
+                        continue
+                    else:
+                        raise ValueError(f"frisk-b200-execute: unsupported op {child.op_name} in an executed kernel")
+
+    visit(kernel, [])
+    if len(found) != 1:
+        raise ValueError(f"frisk-b200-execute: expected exactly one frisk.gemm, found {len(found)}")
+    return found[0]
+
+
+def _kernel_of(module_or_kernel, name=None):
+    if isinstance(module_or_kernel, ir.KernelOp):
+        return module_or_kernel
+    kernels = [op for op in module_or_kernel.regions[0].front().operations if isinstance(op, ir.KernelOp)]
+    if name is not None:
+        kernels = [k for k in kernels if k.attrs["sym_name"] == name]
+    if len(kernels) != 1:
+        raise ValueError(f"frisk-b200-execute: expected one kernel, found {len(kernels)}")
+    return kernels[0]
+
+
+def gemm_plan(module_or_kernel, name=None, algo=capi.ALGO_AUTO):
+    """Host-only: resolve the kernel to (descriptor, (ia, ib, ic)) where the indices name the
+    kernel arguments bound to A, B and C."""
+    kernel = _kernel_of(module_or_kernel, name)
+    if not kernel.verify():
+        raise ValueError("frisk-b200-execute: kernel does not verify")
+    gemm, chain = _find_gemm(kernel)
+    entry = kernel.regions[0].front()
+    idx = []
+    for v in gemm.operands:
+        if not (v.is_arg and v.owner is entry):
+            raise ValueError("frisk-b200-execute: gemm operands must be kernel arguments")
+        if v.type.space != ir.MemorySpace.GLOBAL:
+            raise ValueError("frisk-b200-execute: gemm operands must be global memrefs")
+        idx.append(v.index)
+    a = gemm.attrs
+    if not a["clear_accum"]:
+        trips = 1
+        for op in chain:
+            if isinstance(op, ir.ForOp):
+                trips *= max(0, -(-(op.attrs["upper"] - op.attrs["lower"]) // max(1, op.attrs["step"])))
+        if trips != 1:
+            raise ValueError("frisk-b200-execute: an accumulating gemm inside a multi-trip frisk.for is not a single GEMM")
+    ta, tc = gemm.operands[0].type, gemm.operands[2].type
+    code = {"f16": capi.F16, "bf16": capi.BF16, "f32": capi.F32}
+    if ta.element.name not in code or tc.element.name not in code:
+        raise ValueError("legacy-gemm-type: no B200 kernel for this element type")
+    desc = capi.gemm_desc(a["M"], a["N"], a["K"], code[ta.element.name], code[tc.element.name],
+                          a["transA"], a["transB"], a["clear_accum"], algo=algo)
+    desc.policy = int(a["policy"])
+    return desc, tuple(idx)
+
+
+def execute(module_or_kernel, *tensors, stream=None, name=None, algo=capi.ALGO_AUTO):
+    """Run the kernel on CUDA tensors bound positionally to its memref arguments."""
+    torch = _torch()
+    kernel = _kernel_of(module_or_kernel, name)
+    desc, (ia, ib, ic) = gemm_plan(kernel, algo=algo)
+    arg_types = kernel.attrs["function_type"].inputs
+    if len(tensors) != len(arg_types):
+        raise ValueError(f"frisk-b200-execute: kernel takes {len(arg_types)} tensors, got {len(tensors)}")
+    for t, ty in zip(tensors, arg_types):
+        if t is None:
+            continue
+        if not t.is_cuda:
+            raise ValueError("frisk-b200-execute: tensors must live on a CUDA device (there is no CPU path)")
+        if list(t.shape) != list(ty.shape) or not t.is_contiguous():
+            raise ValueError(f"frisk-b200-execute: tensor of shape {list(t.shape)} does not match {ty}")
+        want = {"f16": torch.float16, "bf16": torch.bfloat16, "f32": torch.float32}.get(ty.element.name)
+        if t.dtype != want:
+            raise ValueError(f"frisk-b200-execute: tensor dtype {t.dtype} does not match {ty}")
+    a, b, c = tensors[ia], tensors[ib], tensors[ic]
+    dev = c.device.index or 0
+    ctx = context_for(dev)
+    ctx.gemm(desc, a.data_ptr(), b.data_ptr(), c.data_ptr(), stream=_stream_ptr(stream, c.device))
+    return c
+
+
+def gemm(a, b, c, *, trans_a=False, trans_b=False, clear_accum=True, algo=capi.ALGO_AUTO, stream=None):
+    """Direct GEMM on CUDA tensors (the op ``create_gemm_op`` describes), bypassing IR."""
+    torch = _torch()
+    code = {torch.float32: capi.F32, torch.float16: capi.F16, torch.bfloat16: capi.BF16}
+    m = a.shape[1] if trans_a else a.shape[0]
+    k = a.shape[0] if trans_a else a.shape[1]
+    n = b.shape[0] if trans_b else b.shape[1]
+    rc, msg = capi.gemm_check_memrefs(list(a.shape), code.get(a.dtype, -1), list(b.shape), code.get(b.dtype, -2),
+                                      list(c.shape), code.get(c.dtype, -3), trans_a, trans_b, m, n, k)
+    if rc:
+        raise ValueError(msg)
+    for t in (a, b, c):
+        if not t.is_cuda or t.stride(-1) != 1:
+            raise ValueError("frisk-b200-execute: operands must be row-major CUDA tensors")
+    desc = capi.gemm_desc(m, n, k, code[a.dtype], code[c.dtype], trans_a, trans_b, clear_accum,
+                          lda=a.stride(0), ldb=b.stride(0), ldc=c.stride(0), algo=algo)
+    ctx = context_for(c.device.index or 0)
+    ctx.gemm(desc, a.data_ptr(), b.data_ptr(), c.data_ptr(), stream=_stream_ptr(stream, c.device))
+    return c
+
+
+def attention_geometry(spec):
+    """Validate a launch spec dict (B, H, N, D [, N_kv]) the way
+    ``tail_attention_reference.geometry`` does for its envelope, for ours."""
+    keys = {"B", "H", "N", "D"}
+    if not isinstance(spec, dict) or not keys <= set(spec) or any(not isinstance(spec[k], int) for k in keys):
+        raise ValueError("expected integer B/H/N/D")
+    if min(spec["B"], spec["H"], spec["N"]) <= 0 or spec["D"] not in (64, 128):
+        raise ValueError("shape outside the attention launch contract")
+    return spec["B"], spec["H"], spec["N"], spec["D"]
+
+
+def attention_forward(spec, q, k, v, out, *, scale=None, causal=False, stream=None):
+    """O = softmax(scale * Q K^T [+causal]) V on compact BHSD CUDA tensors."""
+    torch = _torch()
+    b, h, n, d = attention_geometry(spec)
+    n_kv = int(spec.get("N_kv", n))
+    code = {torch.float32: capi.F32, torch.float16: capi.F16, torch.bfloat16: capi.BF16}
+    for t, s in ((q, n), (k, n_kv), (v, n_kv), (out, n)):
+        if not t.is_cuda or not t.is_contiguous() or list(t.shape) != [b, h, s, d]:
+            raise ValueError("attention operands must be compact BHSD CUDA tensors")
+    if k.dtype != q.dtype or v.dtype != q.dtype or q.dtype not in (torch.float16, torch.bfloat16):
+        raise ValueError("attention inputs must share one 16-bit float type")
+    if scale is None:
+        scale = 1.0 / math.sqrt(d)
+    desc = capi.attn_desc(b, h, n, n_kv, d, scale, causal, code[q.dtype], code[out.dtype])
+    ctx = context_for(out.device.index or 0)
+    ctx.attention_fwd(desc, q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
+                      stream=_stream_ptr(stream, out.device))
+    return out

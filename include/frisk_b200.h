@@ -1,0 +1,166 @@
+/*
+ * libfrisk_b200 — C ABI of the B200 (sm_100a) GEMM / attention kernels that stand in
+ * for the NVIDIA lowering of the Frisk dialect's `frisk.gemm` op and of its attention
+ * graph.  Plain C: pointers and sizes only.  Device pointers are raw 64-bit device
+ * addresses, as in the reference's launcher (benchmark/layout/execution/load_cubin.py:16,
+ * run_execution.py:77).  `stream` is a cudaStream_t passed as void* (NULL = default stream).
+ *
+ * Return value of every int function: 0 = OK; negative = contract violation found on the
+ * host before anything was launched (the reference raises ValueError at the same point,
+ * ffi/ir.cpp:333-341, benchmark/layout/execution/async_host.py:4-10); positive = CUDA /
+ * device-side status.  frisk_b200_strerror() turns a code into text whose prefix matches
+ * the reference's message prefixes ("legacy-gemm-shape", "legacy-gemm-type").
+ *
+ * Ownership: the caller owns every operand buffer and the optional workspace; the
+ * library owns only what hangs off the opaque context (cached TMA descriptors, staging
+ * buffers of the *_host entry points).  Kernels launch on the caller's stream and never
+ * synchronise, except the *_host entry points, which return after the result is in host
+ * memory.  Inputs are read-only and may alias each other; the output must not overlap an
+ * input (benchmark/layout/execution/tiled_execution.py:113-139).
+ */
+#ifndef FRISK_B200_H
+#define FRISK_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct frisk_b200_ctx frisk_b200_ctx;
+
+/* element types: the float types python/frisk/common/utils.py:156-170 can name */
+enum { FRISK_B200_F32 = 0, FRISK_B200_F16 = 1, FRISK_B200_BF16 = 2 };
+
+/* kernel selection for frisk_b200_gemm (AUTO picks by type and shape) */
+enum {
+  FRISK_B200_ALGO_AUTO = 0,
+  FRISK_B200_ALGO_SIMT_F32 = 1, /* fp32 CUDA-core GEMM                                   */
+  FRISK_B200_ALGO_TCGEN05 = 2,  /* fp16/bf16 tcgen05 + TMEM + TMA ring                   */
+  FRISK_B200_ALGO_SKINNY = 3    /* M<=16 weight-streaming GEMM, split-K across CTAs      */
+};
+
+/* error codes (negative: host-side contract checks) */
+enum {
+  FRISK_B200_OK = 0,
+  FRISK_B200_E_GEMM_SHAPE = -1,    /* "legacy-gemm-shape: ..."  */
+  FRISK_B200_E_GEMM_TYPE = -2,     /* "legacy-gemm-type: ..."   */
+  FRISK_B200_E_ALIGN = -3,         /* pointer / pitch not 16-byte aligned                   */
+  FRISK_B200_E_OVERLAP = -4,       /* output overlaps an input                              */
+  FRISK_B200_E_WORKSPACE = -5,     /* workspace missing or too small                        */
+  FRISK_B200_E_UNSUPPORTED = -6,   /* no kernel for this type / layout / algo combination   */
+  FRISK_B200_E_ARG = -7,           /* null pointer, bad enum, bad context                   */
+  FRISK_B200_E_ATTN_SHAPE = -8,    /* attention shape outside the launch contract           */
+  FRISK_B200_E_TOO_LARGE = -9,     /* exceeds the fixed capacity of a no-allocation entry   */
+  FRISK_B200_E_DEVICE_TIMEOUT = 1, /* a bounded device-side wait ran out (status word set)  */
+  FRISK_B200_E_CUDA = 2            /* a CUDA runtime/driver call failed (see last_cuda)     */
+};
+
+/*
+ * GEMM descriptor: the attributes of `frisk.gemm`
+ * (include/Dialect/Frisk/IR/FriskOps.td:252-268: A, B, C, transA, transB, M, N, K, policy,
+ * clear_accum) plus leading dimensions in ELEMENTS (0 = dense).
+ * Buffers are dense row-major memrefs; transposes are flags, not strides
+ * (lib/Dialect/Frisk/IR/LegacyImportSemantics.cpp:37-44):
+ *   A buffer is [M,K] (trans_a=0) or [K,M] (trans_a=1)
+ *   B buffer is [K,N] (trans_b=0) or [N,K] (trans_b=1)
+ *   C buffer is [M,N].
+ * C <- (clear_accum ? 0 : C) + op(A).op(B), fp32 accumulation, one rounding to dtype_c
+ * (lib/Dialect/Frisk/IR/FriskOps.cpp:416-426).
+ */
+typedef struct frisk_b200_gemm_desc {
+  int64_t M, N, K;
+  int32_t trans_a, trans_b;
+  int32_t clear_accum;
+  int32_t dtype_ab; /* FRISK_B200_F32 / F16 / BF16: A and B share it */
+  int32_t dtype_c;  /* == dtype_ab, or F32 for F16/BF16 inputs      */
+  int64_t lda, ldb, ldc;
+  int32_t policy; /* GemmWarpPolicy of the op; informational (kernels fix their own tiling) */
+  int32_t algo;   /* FRISK_B200_ALGO_*                                                        */
+} frisk_b200_gemm_desc;
+
+/*
+ * Attention-forward descriptor.  Q [B,H,S_q,D], K/V [B,H,S_kv,D], O [B,H,S_q,D], compact
+ * BHSD (benchmark/layout/execution/tiled_attention.py:52-55).  O = softmax(scale * Q.K^T
+ * [+ causal mask]).V with fp32 scores and statistics and P rounded to the 16-bit input
+ * type before P.V (tiled_attention.py:628-629, tail_attention_reference.py:74-85).
+ * causal: key j is visible to query i iff j <= i + S_kv - S_q.
+ */
+typedef struct frisk_b200_attn_desc {
+  int32_t B, H, S_q, S_kv, D;
+  float scale;
+  int32_t causal;
+  int32_t dtype_in;  /* F16 or BF16                      */
+  int32_t dtype_out; /* == dtype_in, or F32              */
+} frisk_b200_attn_desc;
+
+/* ---- context -------------------------------------------------------------------------
+ * Replaces the reference's per-run module load (benchmark/layout/execution/load_cubin.py:6).
+ * `device` is a CUDA ordinal; the context caches TMA descriptors and staging buffers. */
+int frisk_b200_ctx_create(frisk_b200_ctx** out, int device);
+int frisk_b200_ctx_destroy(frisk_b200_ctx* ctx);
+/* Device status word of the last launch that was checked (0 = clean) and the last CUDA
+ * error code seen by this context. */
+int frisk_b200_last_status(frisk_b200_ctx* ctx);
+int frisk_b200_last_cuda(frisk_b200_ctx* ctx);
+const char* frisk_b200_strerror(int code);
+const char* frisk_b200_version(void);
+
+/* ---- GEMM ----------------------------------------------------------------------------
+ * Host-only contract check: what ffi/ir.cpp:323-354 (create_gemm_op) does through
+ * getLegacyGemmValidationError (lib/Dialect/Frisk/IR/LegacyImportSemantics.cpp:11-46).
+ * Usable without a GPU. */
+int frisk_b200_gemm_validate(const frisk_b200_gemm_desc* desc);
+/* The same check over the memref SHAPES of the three operands, exactly the test
+ * getLegacyGemmValidationError applies (rank 2, static (>= 0) extents, positive M/N/K,
+ * A/B same type, C same type or f32 for f16/bf16, effective shapes match M/N/K, C is MxN).
+ * `message`, when not NULL, receives the reference's message text (NULL when the check
+ * passes).  Host-only. */
+int frisk_b200_gemm_check_memrefs(int32_t a_rank, const int64_t* a_shape, int32_t a_dtype,
+                                  int32_t b_rank, const int64_t* b_shape, int32_t b_dtype,
+                                  int32_t c_rank, const int64_t* c_shape, int32_t c_dtype,
+                                  int32_t trans_a, int32_t trans_b, int64_t m, int64_t n, int64_t k,
+                                  const char** message);
+/* Which kernel AUTO resolves to for this descriptor (FRISK_B200_ALGO_*), or a negative
+ * error.  Host-only. */
+int frisk_b200_gemm_select(const frisk_b200_gemm_desc* desc);
+/* Bytes of caller-provided, ZERO-INITIALISED scratch this descriptor needs (0 = none).
+ * The kernels leave the control words zero again, so one memset at allocation suffices. */
+size_t frisk_b200_gemm_workspace_bytes(const frisk_b200_gemm_desc* desc);
+/* Replaces the launch of the kernel the reference would have generated for a
+ * `frisk.gemm` (benchmark/layout/execution/run_execution.py:84, load_cubin.py:18). */
+int frisk_b200_gemm(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc* desc, const void* A,
+                    const void* B, void* C, void* workspace, size_t workspace_bytes,
+                    void* stream);
+/* Same op on HOST buffers: copies A, B (and C when it is read) to the device, runs, copies
+ * C back and returns when C is valid.  The end-to-end path of the benchmark. */
+int frisk_b200_gemm_host(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc* desc, const void* A,
+                         const void* B, void* C);
+
+/* ---- attention forward -----------------------------------------------------------------
+ * Replaces the launch of `frisk_execution` for the attention graph
+ * (benchmark/layout/execution/tiled_attention.py:56-61: args q,k,v,out,scratch). */
+int frisk_b200_attention_validate(const frisk_b200_attn_desc* desc);
+size_t frisk_b200_attention_workspace_bytes(const frisk_b200_attn_desc* desc);
+int frisk_b200_attention_fwd(frisk_b200_ctx* ctx, const frisk_b200_attn_desc* desc, const void* Q,
+                             const void* K, const void* V, void* O, void* workspace,
+                             size_t workspace_bytes, void* stream);
+int frisk_b200_attention_fwd_host(frisk_b200_ctx* ctx, const frisk_b200_attn_desc* desc,
+                                  const void* Q, const void* K, const void* V, void* O);
+
+/* ---- split-K epilogue ------------------------------------------------------------------
+ * After the fp32 partial products of a K-split GEMM have been summed across GPUs
+ * (reduce-scatter), round this GPU's slice to the 16-bit output type.  No reference
+ * counterpart: the reference has no multi-GPU path. */
+int frisk_b200_convert_f32(frisk_b200_ctx* ctx, const float* src, void* dst, int64_t count,
+                           int32_t dtype_dst, void* stream);
+
+/* Checks the device status word after the stream has drained (synchronises `stream`).
+ * Returns 0, FRISK_B200_E_DEVICE_TIMEOUT or FRISK_B200_E_CUDA. */
+int frisk_b200_check(frisk_b200_ctx* ctx, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FRISK_B200_H */

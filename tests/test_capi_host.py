@@ -1,0 +1,84 @@
+"""Host-only checks of the C ABI: the library loads, exports every symbol the header
+declares, and its contract checks agree with the oracle's restatement of
+LegacyImportSemantics.cpp:11-46.  No compute call is made here."""
+import itertools
+import pathlib
+import re
+
+from frisk_b200 import capi
+from oracle import gemm_oracle
+
+HEADER = pathlib.Path(__file__).resolve().parents[1] / "include" / "frisk_b200.h"
+
+
+def declared_symbols():
+    text = HEADER.read_text()
+    return sorted(set(re.findall(r"\b(frisk_b200_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_every_declared_symbol_is_exported():
+    lib = capi.load()
+    names = declared_symbols()
+    assert len(names) >= 18
+    for name in names:
+        assert getattr(lib, name) is not None
+    assert set(names) == set(capi.EXPORTS)
+
+
+def test_version_and_strerror():
+    lib = capi.load()
+    assert b"sm_100a" in lib.frisk_b200_version()
+    assert capi.strerror(-1).startswith("legacy-gemm-shape")
+    assert capi.strerror(-2).startswith("legacy-gemm-type")
+    assert capi.strerror(0) == "ok"
+
+
+def test_memref_contract_matches_oracle_restatement():
+    names = {capi.F32: "fp32", capi.F16: "fp16", capi.BF16: "bf16"}
+    shapes = [(64, 16), (16, 64), (64, 64), (8, 64), (64, 8)]
+    n_bad = n_ok = 0
+    for a, b, c in itertools.product(shapes, repeat=3):
+        for ta, tb in itertools.product((0, 1), repeat=2):
+            for da, db, dc in ((1, 1, 1), (1, 1, 0), (2, 2, 0), (1, 2, 0), (0, 0, 1), (0, 0, 0), (2, 2, 1)):
+                m, k = (a[1], a[0]) if ta else a
+                n = b[0] if tb else b[1]
+                code, msg = capi.gemm_check_memrefs(a, da, b, db, c, dc, ta, tb, m, n, k)
+                want = gemm_oracle.validation_error(a, b, c, names[da], names[db], names[dc], ta, tb, m, n, k)
+                assert msg == want, (a, b, c, ta, tb, da, db, dc)
+                assert (code == 0) == (want is None)
+                n_bad += code != 0
+                n_ok += code == 0
+    assert n_bad > 100 and n_ok > 20
+
+
+def test_rank_and_sign_checks():
+    assert capi.gemm_check_memrefs((4,), 1, (4, 4), 1, (4, 4), 1, 0, 0, 4, 4, 4)[1].endswith("must have rank 2")
+    assert capi.gemm_check_memrefs((4, -1), 1, (4, 4), 1, (4, 4), 1, 0, 0, 4, 4, 4)[1].endswith("static shapes")
+    assert capi.gemm_check_memrefs((0, 4), 1, (4, 4), 1, (0, 4), 1, 0, 0, 0, 4, 4)[1].endswith("must be positive")
+
+
+def test_kernel_selection_and_workspace():
+    lib = capi.load()
+    sel = lambda d: lib.frisk_b200_gemm_select(d)  # noqa: E731
+    assert sel(capi.gemm_desc(1024, 1024, 1024, "fp32")) == capi.ALGO_SIMT_F32
+    assert sel(capi.gemm_desc(4096, 4096, 4096, "fp16", trans_b=True)) == capi.ALGO_TCGEN05
+    assert sel(capi.gemm_desc(4096, 4096, 4096, "fp16")) == capi.ALGO_TCGEN05
+    skinny = capi.gemm_desc(16, 28672, 8192, "bf16", trans_b=True)
+    assert sel(skinny) == capi.ALGO_SKINNY
+    assert lib.frisk_b200_gemm_workspace_bytes(skinny) > 0
+    assert lib.frisk_b200_gemm_workspace_bytes(capi.gemm_desc(4096, 4096, 4096, "fp16", trans_b=True)) == 0
+    assert sel(capi.gemm_desc(16, 64, 64, "bf16")) == capi.ALGO_TCGEN05  # weights not K-contiguous
+    assert sel(capi.gemm_desc(64, 64, 60, "bf16", trans_b=True)) == -3   # 120-byte pitch
+    assert sel(capi.gemm_desc(64, 64, 64, "fp32", "fp16")) == -2
+    assert sel(capi.gemm_desc(0, 64, 64, "fp32")) == -1
+    assert sel(capi.gemm_desc(64, 64, 64, "fp16", algo=capi.ALGO_SIMT_F32)) == -6
+
+
+def test_attention_validate():
+    lib = capi.load()
+    ok = capi.attn_desc(8, 32, 4096, 4096, 128, 128 ** -0.5, True, "bf16")
+    assert lib.frisk_b200_attention_validate(ok) == 0
+    assert lib.frisk_b200_attention_validate(capi.attn_desc(1, 1, 64, 64, 96, 0.1, False, "bf16")) == -8
+    assert lib.frisk_b200_attention_validate(capi.attn_desc(1, 1, 64, 64, 64, 0.1, False, "fp32")) == -6
+    assert lib.frisk_b200_attention_validate(capi.attn_desc(1, 1, 128, 64, 64, 0.1, True, "fp16")) == -8
+    assert lib.frisk_b200_attention_validate(capi.attn_desc(1, 1, 64, 64, 64, 0.125, False, "fp16", "fp32")) == 0

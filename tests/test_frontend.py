@@ -1,0 +1,158 @@
+"""The re-hosted builder surface: the flows of the reference's test/python/bind_test.py,
+helper_test.py and legacy_normalization_test.py:82-88, minus what needs frisk-opt."""
+import pytest
+
+import frisk_b200 as F
+
+
+def build_bind_test_module(clear_accum=False, with_side_ops=True, dtype_name="f16", shape=(4096, 4096)):
+    context = F.context()
+    F.frisk.load_dialects(context)
+    builder = F.builder(context)
+    module = builder.create_module()
+    module.context = context
+    dtype = {"f16": builder.get_f16_ty, "bf16": builder.get_bf16_ty, "f32": builder.get_f32_ty}[dtype_name]()
+    mem_type = builder.get_memref_ty(dtype, list(shape), F.AffineMap(), F.MemorySpace.GLOBAL)
+    mem2_type = builder.get_memref_ty(dtype, [shape[0]], F.AffineMap(), F.MemorySpace.GLOBAL)
+    kernel_type = builder.get_kernel_ty([mem_type, mem_type, mem_type, mem2_type])
+    kernel = builder.create_kernel_op(module, "test_gemm", kernel_type)
+    module.push_back(kernel)
+    entry1 = kernel.add_entry_block()
+    builder.set_insertion_point_to_start(entry1)
+    parallel = builder.create_parallel_op([8, 8], 128)
+    entry2 = parallel.add_entry_block()
+    builder.set_insertion_point_to_start(entry2)
+    args = [entry1.get_argument(i) for i in range(4)]
+    builder.create_alloc_buffer_op([128, 32], "fp16", F.MemorySpace.SHARED, 1024)
+    builder.create_alloc_buffer_op([32, 128], "fp16", F.MemorySpace.SHARED, 1024)
+    builder.create_alloc_buffer_op([128, 128], "fp16", F.MemorySpace.LOCAL)
+
+    def for_body(b, iv):
+        if with_side_ops:
+            builder.create_fill_op(args[0], 0.0, "fp16")
+            builder.create_reduce_op(args[0], args[3], "max", 1, True)
+            builder.create_copy_op(args[0], args[1], [iv, iv], [iv, iv])
+
+        def block_body(b, ivs):
+            assert len(ivs) == 2
+            b.create_gemm_op(args[0], args[1], args[2], False, False, clear_accum)
+        builder.create_block_op([128, 128], block_body)
+    builder.create_for_op(0, 128, 1, for_body)
+    return module
+
+
+def test_bind_test_flow_prints_the_ops():
+    text = str(build_bind_test_module())
+    assert "frisk.kernel @test_gemm(memref<4096x4096xf16, 1>" in text
+    assert "frisk.parallel (%arg4, %arg5) = (8, 8), threads = 128 {" in text
+    assert "frisk.alloc_buffer {alignment = 1024 : i64} -> memref<128x32xf16, 3>" in text
+    assert "-> memref<128x128xf16>" in text  # LOCAL = space 0 is elided
+    assert "frisk.for %arg6 = 0 to 128 {" in text
+    assert "frisk.block (%arg7, %arg8) to (128, 128) {" in text
+    assert ("frisk.gemm(%arg0, %arg1, %arg2) {K = 4096 : i64, M = 4096 : i64, N = 4096 : i64, "
+            "clear_accum = false, policy = #frisk<gemm_warp_policy Square>, transA = false, transB = false}") in text
+    assert 'frisk.reduce %arg0, %arg3 {clear = true, dim = 1 : i64, kind = "max"}' in text
+    assert "frisk.copy %arg0[%arg6, %arg6], %arg1[%arg6, %arg6]" in text
+
+
+def test_helper_demo_flow():
+    helper = F.create_session()
+    f16 = helper.builder.get_f16_ty()
+    a_ty = helper.memref_type((128, 64), f16, space=F.MemorySpace.SHARED)
+    b_ty = helper.memref_type((64, 128), f16, space=F.MemorySpace.SHARED)
+    c_ty = helper.memref_type((128, 128), f16, space=F.MemorySpace.LOCAL)
+    kernel, entry = helper.new_kernel("helper_demo", [a_ty, b_ty, c_ty])
+    args = [entry.get_argument(i) for i in range(3)]
+    gemm = helper.create_gemm(args[0], args[1], args[2])
+    assert gemm.get_matrix_A() is args[0] and gemm.get_matrix_C() is args[2]
+    scratch = helper.alloc_buffer((32, 32), "fp16", space=F.MemorySpace.SHARED, alignment=64)
+    assert "memref" in str(scratch.get_type())
+    assert kernel.verify()
+    assert helper.module.verify()
+    assert helper.module.context is helper.context
+
+
+def test_builder_rejects_effective_shape_mismatch():
+    session = F.create_session()
+    _, entry = session.new_kernel("bad", [session.memref_type([64, 16]), session.memref_type([8, 64]),
+                                          session.memref_type([64, 64], "fp32")])
+    with pytest.raises(ValueError, match="legacy-gemm-shape"):
+        session.create_gemm(*(entry.get_argument(i) for i in range(3)))
+
+
+def test_builder_type_contract():
+    session = F.create_session()
+    _, e = session.new_kernel("t", [session.memref_type([64, 16], "fp16"), session.memref_type([16, 64], "bf16"),
+                                    session.memref_type([64, 64], "fp32"), session.memref_type([16, 64], "fp16"),
+                                    session.memref_type([64, 64], "bf16")])
+    with pytest.raises(ValueError, match="legacy-gemm-type: A and B must have the same element type"):
+        session.create_gemm(e.get_argument(0), e.get_argument(1), e.get_argument(2))
+    with pytest.raises(ValueError, match="legacy-gemm-type: C must match"):
+        session.create_gemm(e.get_argument(0), e.get_argument(3), e.get_argument(4))
+    # f16 x f16 -> f32 and f16 x f16 -> f16 are both in the contract
+    session.create_gemm(e.get_argument(0), e.get_argument(3), e.get_argument(2))
+
+
+def test_all_transposes_derive_mnk():
+    for ta in (False, True):
+        for tb in (False, True):
+            s = F.create_session()
+            a = [16, 64] if ta else [64, 16]
+            b = [32, 16] if tb else [16, 32]
+            _, e = s.new_kernel("g", [s.memref_type(a), s.memref_type(b), s.memref_type([64, 32], "fp32")])
+            op = s.create_gemm(e.get_argument(0), e.get_argument(1), e.get_argument(2), trans_a=ta, trans_b=tb,
+                               clear_accum=True, legacy_semantics="tensor_v1")
+            assert (op.attrs["M"], op.attrs["N"], op.attrs["K"]) == (64, 32, 16)
+            assert 'frisk.legacy_semantics = "tensor_v1"' in str(s.module)
+
+
+def test_api_quirks():
+    s = F.create_session()
+    kernel, entry = s.new_kernel("k", [s.memref_type([8, 8])])
+    # create_parallel_op must be the first thing built in the kernel body
+    s.builder.create_alloc_buffer_op([8, 8], "fp16")
+    with pytest.raises(ValueError, match="invalid parallel create"):
+        s.builder.create_parallel_op([1], 128)
+    # create_kernel_op returns the existing op for a known symbol
+    again = s.builder.create_kernel_op(s.module, "k", s.builder.get_kernel_ty([]))
+    assert again is kernel
+    with pytest.raises(ValueError, match="invalid float type"):
+        s.builder.create_alloc_buffer_op([8], "bf16")  # the string set has no bf16 in the reference either
+    with pytest.raises(ValueError, match="alignment must be non-negative"):
+        s.builder.create_alloc_buffer_op([8], "fp16", F.MemorySpace.SHARED, -1)
+    with pytest.raises(IndexError):
+        entry.get_argument(5)
+    # thread-count whitelist and power-of-two alignment are verifier errors
+    s2 = F.create_session()
+    k2, e2 = s2.new_kernel("p", [])
+    par = s2.builder.create_parallel_op([2], 96)
+    par.add_entry_block()
+    assert not k2.verify()
+    s3 = F.create_session()
+    k3, _ = s3.new_kernel("q", [])
+    s3.builder.create_alloc_buffer_op([8], "fp16", F.MemorySpace.SHARED, 24)
+    assert not k3.verify()
+
+
+def test_gemm_plan_from_bind_test_nest():
+    # an idempotent gemm (clear_accum) inside parallel/for/block resolves to one GEMM
+    mod = build_bind_test_module(clear_accum=True, with_side_ops=False)
+    desc, idx = F.gemm_plan(mod)
+    assert (desc.M, desc.N, desc.K) == (4096, 4096, 4096)
+    assert (desc.trans_a, desc.trans_b, desc.clear_accum) == (0, 0, 1)
+    assert idx == (0, 1, 2)
+    assert desc.dtype_ab == F.capi.F16 and desc.dtype_c == F.capi.F16
+    # accumulate inside a 128-trip loop is not one GEMM; side-effecting neighbours are refused
+    with pytest.raises(ValueError, match="multi-trip"):
+        F.gemm_plan(build_bind_test_module(clear_accum=False, with_side_ops=False))
+    with pytest.raises(ValueError, match="unsupported op frisk.fill"):
+        F.gemm_plan(build_bind_test_module(clear_accum=True, with_side_ops=True))
+
+
+def test_execute_refuses_cpu_tensors():
+    import torch
+    mod = build_bind_test_module(clear_accum=True, with_side_ops=False, shape=(128, 128))
+    t = torch.zeros(128, 128, dtype=torch.float16)
+    v = torch.zeros(128, dtype=torch.float16)
+    with pytest.raises(ValueError, match="no CPU path"):
+        F.execute(mod, t, t, t.clone(), v)
