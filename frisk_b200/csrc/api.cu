@@ -117,6 +117,23 @@ int ensure_stage(frisk_b200_ctx* ctx, int slot, size_t bytes, bool zero) {
   return 0;
 }
 
+// Library-owned skinny-GEMM scratch: allocated (zeroed) on demand; its control prefix is
+// cleared on the launch stream whenever the control layout differs from the last use.
+int prepare_owned_skinny_ws(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc& d, cudaStream_t s) {
+  size_t need = skinny_workspace_bytes(d);
+  void* before = ctx->stage[3].ptr;
+  int rc = ensure_stage(ctx, 3, need, true);
+  if (rc) return rc;
+  uint64_t sig = skinny_layout_signature(d);
+  if (ctx->stage[3].ptr != before) {
+    ctx->ws_signature = sig;  // fresh and fully zeroed
+  } else if (ctx->ws_signature != sig) {
+    FB_CUDA(ctx, cudaMemsetAsync(ctx->stage[3].ptr, 0, skinny_control_bytes(d), s));
+    ctx->ws_signature = sig;
+  }
+  return 0;
+}
+
 bool ranges_overlap(const void* a, size_t an, const void* b, size_t bn) {
   uintptr_t a0 = reinterpret_cast<uintptr_t>(a), b0 = reinterpret_cast<uintptr_t>(b);
   return a0 < b0 + bn && b0 < a0 + an;
@@ -326,7 +343,8 @@ int frisk_b200_gemm(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc* d, const vo
       if (!workspace) {
         // library-owned scratch: zeroed when (re)allocated, left clean by every launch
         std::lock_guard<std::mutex> lock(ctx->mu);
-        int rc = ensure_stage(ctx, 3, need, true);
+        (void)need;
+        int rc = prepare_owned_skinny_ws(ctx, *d, s);
         if (rc) return rc;
         workspace = ctx->stage[3].ptr;
         workspace_bytes = ctx->stage[3].bytes;
@@ -351,9 +369,8 @@ int frisk_b200_gemm_host(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc* d, con
   if ((rc = ensure_stage(ctx, 0, e.a, false))) return rc;
   if ((rc = ensure_stage(ctx, 1, e.b, false))) return rc;
   if ((rc = ensure_stage(ctx, 2, e.c, false))) return rc;
-  size_t need = frisk_b200_gemm_workspace_bytes(d);
-  if (need && (rc = ensure_stage(ctx, 3, need, true))) return rc;
   cudaStream_t s = ctx->host_stream, s2 = ctx->copy_stream;
+  if (algo == FRISK_B200_ALGO_SKINNY && (rc = prepare_owned_skinny_ws(ctx, *d, s))) return rc;
   // A and B travel on two streams so that both copy engines are used
   FB_CUDA(ctx, cudaMemcpyAsync(ctx->stage[0].ptr, A, e.a, cudaMemcpyHostToDevice, s));
   FB_CUDA(ctx, cudaMemcpyAsync(ctx->stage[1].ptr, B, e.b, cudaMemcpyHostToDevice, s2));

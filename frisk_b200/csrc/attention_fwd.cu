@@ -1,8 +1,437 @@
-// placeholder until the fused attention kernel lands
+// Fused attention forward for sm_100a: O = softmax(scale * Q.K^T [+ causal mask]) . V over
+// compact BHSD tensors, fp16/bf16 inputs, fp32 scores and statistics, probabilities rounded to
+// the 16-bit input type before P.V.  Numerics contract:
+// benchmark/layout/execution/tiled_attention.py:392,505-515,628-629 (scale applied to the fp32
+// dot, exp through ex2, P rounded RNE before P.V, fp32 accumulation of P.V); launch contract:
+// tiled_attention.py:52-61 (compact BHSD, q/k/v/out pointers).
+//
+// Unlike the reference's three-pass schedule (tiled_attention.py:697-698) this is a single
+// pass with an online softmax, so K and V are read once per query tile:
+//
+//   * one CTA owns TWO 128-row query tiles of one (batch, head) and streams 128-key K/V tiles
+//     through a 2-stage TMA ring (K and V have separate full/empty mbarriers);
+//   * warp 0 is the TMA producer, warp 1 issues every tcgen05.mma: S_q = Q_q.K^T (SS form,
+//     both operands K-major, 128-byte swizzle) into tensor memory and O_q += P_q.V (P read
+//     from tensor memory, V as an MN-major shared-memory operand);
+//   * warps 2-5 and 6-9 are the two softmax groups: thread r owns row r of its query tile
+//     (TMEM lane r), so row max / row sum need no shuffles.  The two groups alternate, so
+//     the tensor core works on one tile's MMAs while the other group exponentiates;
+//   * the running maximum is applied lazily: O is rescaled in tensor memory only when the
+//     maximum grew by more than 2^8, which keeps P within bf16/fp16 range and makes most
+//     iterations rescale-free;
+//   * causal: key tiles wholly above the diagonal are never loaded; only tiles that touch the
+//     diagonal (or the ragged end of the keys) are masked.
+// TMEM columns: S0 [0,128) S1 [128,256) O0 [256,256+D) O1 [384,384+D); P_q aliases the first
+// 64 columns of S_q (two 16-bit values per column).
+// Every mbarrier wait is bounded (ptx.cuh); no TMA load uses cluster multicast.
 #include "common.cuh"
+#include "ptx.cuh"
+
 namespace fb {
-int launch_attention_fwd(frisk_b200_ctx*, const frisk_b200_attn_desc&, const void*, const void*, const void*,
-                         void*, cudaStream_t) {
-  return FRISK_B200_E_UNSUPPORTED;
+namespace {
+
+constexpr int BM = 128;        // query rows per tile (two tiles per CTA)
+constexpr int BN = 128;        // keys per K/V tile
+constexpr int kStagesKV = 2;
+constexpr int kThreads = 320;  // TMA warp, MMA warp, 2 x 4 softmax warps
+constexpr float kRescaleThreshold = 8.0f;  // log2 units
+
+enum : unsigned { ST_ATTN_S = 0x201, ST_ATTN_P = 0x202, ST_ATTN_O = 0x203, ST_ATTN_KV = 0x204, ST_ATTN_Q = 0x205 };
+
+template <int D>
+struct AttnSmem {
+  static constexpr int kTileBytes = BM * D * 2;       // one Q, K or V tile
+  static constexpr int kQ = 0;                         // Q0, Q1
+  static constexpr int kK = 2 * kTileBytes;            // K stages
+  static constexpr int kV = kK + kStagesKV * kTileBytes;
+  static constexpr int kBar = kV + kStagesKV * kTileBytes;
+  static constexpr int kTotal = kBar + 256 + 1024;
+};
+
+struct AttnParams {
+  int S_q, S_kv, n_pairs, causal;
+  int64_t total_ctas;
+  float scale_log2;
+  void* O;
+  unsigned* status;
+};
+
+__device__ __forceinline__ float ex2f(float x) {
+  float y;
+  asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
 }
+
+template <bool BF16>
+__device__ __forceinline__ uint32_t pack16(float a, float b) {
+  if (BF16) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&h);
+  } else {
+    __half2 h = __floats2half2_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&h);
+  }
+}
+
+// number of key tiles query tile `m0` needs
+__device__ __forceinline__ int kv_tiles_for(int m0, int S_q, int S_kv, int causal) {
+  if (m0 >= S_q) return 0;
+  int all = (S_kv + BN - 1) / BN;
+  if (!causal) return all;
+  int last_key = min(S_kv - 1, m0 + BM - 1 + (S_kv - S_q));  // visible to the tile's last row
+  return min(all, last_key / BN + 1);
+}
+
+template <bool BF16, int D, bool OUT_F32>
+__global__ void __launch_bounds__(kThreads, 1)
+    attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                         const __grid_constant__ CUtensorMap tmap_v, const AttnParams p) {
+  using L = AttnSmem<D>;
+  constexpr int kBoxes = D / 64;            // 64-element (128-byte) column blocks per tile
+  constexpr int kBoxBytes = BM * 128;       // one [128 rows][128 B] block
+  extern __shared__ unsigned char smem_unaligned[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>(
+      (reinterpret_cast<uintptr_t>(smem_unaligned) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBar);
+  uint64_t* q_full = bars;              // [1]
+  uint64_t* k_full = bars + 1;          // [2]
+  uint64_t* k_empty = bars + 3;         // [2]
+  uint64_t* v_full = bars + 5;          // [2]
+  uint64_t* v_empty = bars + 7;         // [2]
+  uint64_t* s_full = bars + 9;          // [2] per query tile
+  uint64_t* p_ready = bars + 11;        // [2]
+  uint64_t* o_done = bars + 13;         // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int pair = p.n_pairs - 1 - (int)(blockIdx.x % p.n_pairs);  // heavy (late) query tiles first
+  const int bh = (int)(blockIdx.x / p.n_pairs);
+  const int m0 = pair * 2 * BM;
+  const int nq[2] = {kv_tiles_for(m0, p.S_q, p.S_kv, p.causal), kv_tiles_for(m0 + BM, p.S_q, p.S_kv, p.causal)};
+  const int n_max = max(nq[0], nq[1]);
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&k_full[i], 1);
+      mbar_init(&k_empty[i], 1);
+      mbar_init(&v_full[i], 1);
+      mbar_init(&v_empty[i], 1);
+      mbar_init(&s_full[i], 1);
+      mbar_init(&p_ready[i], 128);
+      mbar_init(&o_done[i], 1);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmap_q);
+    tma_prefetch_desc(&tmap_k);
+    tma_prefetch_desc(&tmap_v);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0 && n_max > 0) {
+      mbar_expect_tx(q_full, 2 * L::kTileBytes);
+#pragma unroll
+      for (int q = 0; q < 2; ++q)
+#pragma unroll
+        for (int b = 0; b < kBoxes; ++b)
+          tma_load_3d(smem + L::kQ + q * L::kTileBytes + b * kBoxBytes, &tmap_q, q_full, b * 64, m0 + q * BM, bh);
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int j = 0; j < n_max; ++j) {
+        if (!mbar_wait(&k_empty[stage], phase ^ 1, abort_flag, p.status, ST_ATTN_KV)) break;
+        mbar_expect_tx(&k_full[stage], L::kTileBytes);
+#pragma unroll
+        for (int b = 0; b < kBoxes; ++b)
+          tma_load_3d(smem + L::kK + stage * L::kTileBytes + b * kBoxBytes, &tmap_k, &k_full[stage], b * 64,
+                      j * BN, bh);
+        if (!mbar_wait(&v_empty[stage], phase ^ 1, abort_flag, p.status, ST_ATTN_KV)) break;
+        mbar_expect_tx(&v_full[stage], L::kTileBytes);
+#pragma unroll
+        for (int b = 0; b < kBoxes; ++b)
+          tma_load_3d(smem + L::kV + stage * L::kTileBytes + b * kBoxBytes, &tmap_v, &v_full[stage], b * 64,
+                      j * BN, bh);
+        if (++stage == kStagesKV) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0 && n_max > 0) {
+      constexpr uint32_t idesc_s = umma_idesc_f16(BM, BN, BF16, false, false);
+      constexpr uint32_t idesc_o = umma_idesc_f16(BM, D, BF16, false, true);
+      const uint32_t sq = smem_u32(smem + L::kQ), sk = smem_u32(smem + L::kK), sv = smem_u32(smem + L::kV);
+      bool ok = mbar_wait(q_full, 0, abort_flag, p.status, ST_ATTN_Q);
+      tc_fence_after_sync();
+
+      auto issue_s = [&](int q, int stage) {
+        const uint32_t d_tmem = tmem_base + q * 128;
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (kk / 4) * kBoxBytes + (kk % 4) * 32;
+          umma_f16_ss(d_tmem, umma_desc_kmajor_sw128(sq + q * L::kTileBytes + off),
+                      umma_desc_kmajor_sw128(sk + stage * L::kTileBytes + off), idesc_s, kk != 0);
+        }
+        umma_commit(&s_full[q]);
+      };
+      auto issue_pv = [&](int q, int stage, int j) {
+        const uint32_t d_tmem = tmem_base + 256 + q * 128;
+        const uint32_t a_tmem = tmem_base + q * 128;  // P_q: 8 columns per k16 slice
+#pragma unroll
+        for (int kk = 0; kk < BN / 16; ++kk)
+          umma_f16_ts(d_tmem, a_tmem + kk * 8,
+                      umma_desc_mnmajor_sw128(sv + stage * L::kTileBytes + kk * 2048, kBoxBytes, 1024), idesc_o,
+                      (j | kk) != 0);
+        umma_commit(&o_done[q]);
+      };
+
+      int v_waited = 0;  // V tiles [0, v_waited) are known to have landed
+      auto ensure_v = [&](int j) {
+        while (ok && v_waited <= j) {
+          ok = mbar_wait(&v_full[v_waited % kStagesKV], (v_waited / kStagesKV) & 1, abort_flag, p.status,
+                         ST_ATTN_KV);
+          ++v_waited;
+        }
+        tc_fence_after_sync();
+      };
+
+      for (int j = 0; j < n_max && ok; ++j) {
+        const int stage = j % kStagesKV;
+        ok = mbar_wait(&k_full[stage], (j / kStagesKV) & 1, abort_flag, p.status, ST_ATTN_KV);
+        if (!ok) break;
+        tc_fence_after_sync();
+        if (j < nq[0]) issue_s(0, stage);
+        if (j >= 1 && j - 1 < nq[1]) {  // O1 += P1(j-1) . V(j-1)
+          ok = mbar_wait(&p_ready[1], (j - 1) & 1, abort_flag, p.status, ST_ATTN_P);
+          ensure_v(j - 1);
+          if (!ok) break;
+          tc_fence_after_sync();
+          issue_pv(1, (j - 1) % kStagesKV, j - 1);
+        }
+        if (j >= 1) umma_commit(&v_empty[(j - 1) % kStagesKV]);  // both P.V of tile j-1 are issued
+        if (j < nq[1]) issue_s(1, stage);
+        umma_commit(&k_empty[stage]);  // both S of tile j are issued
+        if (j < nq[0]) {               // O0 += P0(j) . V(j)
+          ok = mbar_wait(&p_ready[0], j & 1, abort_flag, p.status, ST_ATTN_P);
+          ensure_v(j);
+          if (!ok) break;
+          tc_fence_after_sync();
+          issue_pv(0, stage, j);
+        }
+      }
+      if (ok && n_max >= 1) {
+        const int j = n_max - 1;
+        if (j < nq[1]) {
+          ok = mbar_wait(&p_ready[1], j & 1, abort_flag, p.status, ST_ATTN_P);
+          ensure_v(j);
+          if (ok) {
+            tc_fence_after_sync();
+            issue_pv(1, j % kStagesKV, j);
+          }
+        }
+        umma_commit(&v_empty[j % kStagesKV]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax groups
+    const int q = (warp - 2) >> 2;   // query tile of this group
+    const int quad = warp & 3;       // TMEM lane quadrant this warp may touch
+    const int row = quad * 32 + lane;
+    const int n_tiles = nq[q];
+    const int m_tile = m0 + q * BM;
+    const int g_row = m_tile + row;  // query index within the head
+    const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
+    const uint32_t t_s = tmem_base + q * 128 + lane_addr;
+    const uint32_t t_o = tmem_base + 256 + q * 128 + lane_addr;
+    const int off = p.S_kv - p.S_q;
+
+    float m_ref = -INFINITY;  // reference maximum (scaled, log2 units) the stored P and O are relative to
+    float l_sum = 0.f;
+    bool ok = true;
+
+    for (int j = 0; j < n_tiles; ++j) {
+      if (!mbar_wait(&s_full[q], j & 1, abort_flag, p.status, ST_ATTN_S)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after_sync();
+      uint32_t sr[128];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld_32x32b_x32(t_s + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&sr[c * 32]));
+      tmem_ld_wait();
+
+      const int n0 = j * BN;
+      const bool needs_mask = (n0 + BN > p.S_kv) || (p.causal && (n0 + BN - 1 > m_tile + off));
+      float mx = -INFINITY;
+      if (needs_mask) {
+        int limit = p.S_kv - 1;
+        if (p.causal) limit = min(limit, g_row + off);
+        limit -= n0;  // columns > limit are hidden
+#pragma unroll
+        for (int c = 0; c < 128; ++c) {
+          float s = (c > limit) ? -INFINITY : __uint_as_float(sr[c]);
+          sr[c] = __float_as_uint(s);
+          mx = fmaxf(mx, s);
+        }
+      } else {
+#pragma unroll
+        for (int c = 0; c < 128; ++c) mx = fmaxf(mx, __uint_as_float(sr[c]));
+      }
+      float m_new = fmaxf(m_ref, mx * p.scale_log2);
+      if (m_new == -INFINITY) m_new = 0.f;  // a row that sees no key yet: keep everything finite
+
+      // lazy rescale: warp-uniform decision because the TMEM accesses are warp-collective
+      const bool grow = (j > 0) && (m_new - m_ref > kRescaleThreshold);
+      if (j == 0) {
+        m_ref = m_new;
+      } else if (__any_sync(0xffffffffu, grow)) {
+        const float factor = ex2f(m_ref - m_new);
+        m_ref = m_new;
+        l_sum *= factor;
+        // O_q must be complete up to tile j-1 before it is scaled
+        if (!mbar_wait(&o_done[q], (j - 1) & 1, abort_flag, p.status, ST_ATTN_O)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t o[32];
+          tmem_ld_32x32b_x32(t_o + c * 32, o);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * factor);
+          tmem_st_32x32b_x32(t_o + c * 32, o);
+        }
+      }
+
+      // P = 2^(s*scale_log2 - m_ref), row sum in fp32, P rounded to 16 bits for the MMA
+      const float neg_m = -m_ref;
+      float sum0 = 0.f, sum1 = 0.f;
+      uint32_t pk[64];
+#pragma unroll
+      for (int c = 0; c < 64; ++c) {
+        float p0 = ex2f(fmaf(__uint_as_float(sr[2 * c]), p.scale_log2, neg_m));
+        float p1 = ex2f(fmaf(__uint_as_float(sr[2 * c + 1]), p.scale_log2, neg_m));
+        sum0 += p0;
+        sum1 += p1;
+        pk[c] = pack16<BF16>(p0, p1);
+      }
+      l_sum += sum0 + sum1;
+      tmem_st_32x32b_x32(t_s, *reinterpret_cast<uint32_t(*)[32]>(&pk[0]));
+      tmem_st_32x32b_x32(t_s + 32, *reinterpret_cast<uint32_t(*)[32]>(&pk[32]));
+      tmem_st_wait();
+      tc_fence_before_sync();
+      mbar_arrive(&p_ready[q]);
+    }
+
+    // ---- epilogue: O / l
+    if (ok && n_tiles > 0 && mbar_wait(&o_done[q], (n_tiles - 1) & 1, abort_flag, p.status, ST_ATTN_O)) {
+      tc_fence_after_sync();
+      const float inv = 1.0f / l_sum;
+      const bool valid = g_row < p.S_q;
+      const size_t row_off = ((size_t)bh * p.S_q + (size_t)min(g_row, p.S_q - 1)) * D;
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t o[32];
+        tmem_ld_32x32b_x32(t_o + c * 32, o);
+        tmem_ld_wait();
+        if (valid) {
+          if (OUT_F32) {
+            float4* dst = reinterpret_cast<float4*>(static_cast<float*>(p.O) + row_off + c * 32);
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              dst[i] = make_float4(__uint_as_float(o[4 * i]) * inv, __uint_as_float(o[4 * i + 1]) * inv,
+                                   __uint_as_float(o[4 * i + 2]) * inv, __uint_as_float(o[4 * i + 3]) * inv);
+          } else {
+            uint4* dst = reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.O) + row_off + c * 32);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              uint4 v;
+              v.x = pack16<BF16>(__uint_as_float(o[8 * i]) * inv, __uint_as_float(o[8 * i + 1]) * inv);
+              v.y = pack16<BF16>(__uint_as_float(o[8 * i + 2]) * inv, __uint_as_float(o[8 * i + 3]) * inv);
+              v.z = pack16<BF16>(__uint_as_float(o[8 * i + 4]) * inv, __uint_as_float(o[8 * i + 5]) * inv);
+              v.w = pack16<BF16>(__uint_as_float(o[8 * i + 6]) * inv, __uint_as_float(o[8 * i + 7]) * inv);
+              dst[i] = v;
+            }
+          }
+        }
+      }
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  if (*abort_flag) {
+    unsigned long long t0 = globaltimer();
+    while (globaltimer() - t0 < 200000ull) __nanosleep(1000);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+template <bool BF16, int D, bool OUT_F32>
+int launch_cfg(frisk_b200_ctx* ctx, const frisk_b200_attn_desc& d, const void* Q, const void* K, const void* V,
+               void* O, cudaStream_t s) {
+  CUtensorMap tq, tk, tv;
+  const int bh = d.B * d.H;
+  const uint64_t row_bytes = (uint64_t)D * 2;
+  int rc = encode_tmap_3d(&tq, d.dtype_in, Q, D, d.S_q, bh, row_bytes, row_bytes * d.S_q, 64, BM, 1, true);
+  if (!rc) rc = encode_tmap_3d(&tk, d.dtype_in, K, D, d.S_kv, bh, row_bytes, row_bytes * d.S_kv, 64, BN, 1, true);
+  if (!rc) rc = encode_tmap_3d(&tv, d.dtype_in, V, D, d.S_kv, bh, row_bytes, row_bytes * d.S_kv, 64, BN, 1, true);
+  if (rc) {
+    ctx->last_cuda = rc;
+    return FRISK_B200_E_CUDA;
+  }
+  AttnParams p;
+  p.S_q = d.S_q;
+  p.S_kv = d.S_kv;
+  p.n_pairs = (d.S_q + 2 * BM - 1) / (2 * BM);
+  p.causal = d.causal ? 1 : 0;
+  p.total_ctas = (int64_t)p.n_pairs * bh;
+  p.scale_log2 = d.scale * 1.4426950408889634f;
+  p.O = O;
+  p.status = ctx->d_status;
+  if (p.total_ctas > INT32_MAX) return FRISK_B200_E_ATTN_SHAPE;
+  auto kern = attention_fwd_kernel<BF16, D, OUT_F32>;
+  using L = AttnSmem<D>;
+  FB_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
+  kern<<<(unsigned)p.total_ctas, kThreads, L::kTotal, s>>>(tq, tk, tv, p);
+  FB_CUDA(ctx, cudaGetLastError());
+  return 0;
+}
+
+template <bool BF16, int D>
+int launch_out(frisk_b200_ctx* ctx, const frisk_b200_attn_desc& d, const void* Q, const void* K, const void* V,
+               void* O, cudaStream_t s) {
+  if (d.dtype_out == FRISK_B200_F32) return launch_cfg<BF16, D, true>(ctx, d, Q, K, V, O, s);
+  return launch_cfg<BF16, D, false>(ctx, d, Q, K, V, O, s);
+}
+
+}  // namespace
+
+int launch_attention_fwd(frisk_b200_ctx* ctx, const frisk_b200_attn_desc& d, const void* Q, const void* K,
+                         const void* V, void* O, cudaStream_t s) {
+  const bool bf = d.dtype_in == FRISK_B200_BF16;
+  if (d.D == 128) return bf ? launch_out<true, 128>(ctx, d, Q, K, V, O, s) : launch_out<false, 128>(ctx, d, Q, K, V, O, s);
+  if (d.D == 64) return bf ? launch_out<true, 64>(ctx, d, Q, K, V, O, s) : launch_out<false, 64>(ctx, d, Q, K, V, O, s);
+  return FRISK_B200_E_ATTN_SHAPE;
+}
+
 }  // namespace fb

@@ -31,6 +31,7 @@ struct frisk_b200_ctx {
   int num_sms = fb::kNumSMsDefault;
   int last_cuda = 0;
   int last_status = 0;
+  uint64_t ws_signature = 0;     // layout of the control words last left in stage[3]
   unsigned* d_status = nullptr;  // device status word (first failing wait records its code)
   unsigned* h_status = nullptr;  // pinned mirror
   // staging for the *_host entry points and library-owned workspace
@@ -72,6 +73,11 @@ int launch_gemm_simt_f32(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc& d, con
                          float* C, cudaStream_t s);
 
 size_t skinny_workspace_bytes(const frisk_b200_gemm_desc& d);
+// bytes at the start of the workspace that hold control words (must be zero before a launch)
+// and a value that identifies their layout: a workspace last used with another layout must
+// have that prefix cleared again, because partial sums may lie where tickets are expected.
+size_t skinny_control_bytes(const frisk_b200_gemm_desc& d);
+uint64_t skinny_layout_signature(const frisk_b200_gemm_desc& d);
 bool skinny_supported(const frisk_b200_gemm_desc& d);
 int launch_gemm_skinny(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc& d, const void* A, const void* B, void* C,
                        void* ws, size_t ws_bytes, cudaStream_t s);

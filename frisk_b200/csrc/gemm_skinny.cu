@@ -261,6 +261,11 @@ bool skinny_supported(const frisk_b200_gemm_desc& d) {
 size_t skinny_workspace_bytes(const frisk_b200_gemm_desc& d) {
   return make_plan(d, kNumSMsDefault).ws_bytes;
 }
+size_t skinny_control_bytes(const frisk_b200_gemm_desc& d) { return make_plan(d, kNumSMsDefault).off_partials; }
+uint64_t skinny_layout_signature(const frisk_b200_gemm_desc& d) {
+  SkinnyPlan p = make_plan(d, kNumSMsDefault);
+  return (static_cast<uint64_t>(p.ngroups) << 8) | static_cast<uint64_t>(p.S) | (1ull << 63);
+}
 
 // Also used by the fixed-capacity entry point, which passes its own scratch.
 int launch_gemm_skinny(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc& d, const void* A, const void* B, void* C,

@@ -126,7 +126,12 @@ int frisk_b200_gemm_check_memrefs(int32_t a_rank, const int64_t* a_shape, int32_
  * error.  Host-only. */
 int frisk_b200_gemm_select(const frisk_b200_gemm_desc* desc);
 /* Bytes of caller-provided, ZERO-INITIALISED scratch this descriptor needs (0 = none).
- * The kernels leave the control words zero again, so one memset at allocation suffices. */
+ * The kernels leave their control words zero again, so one memset at allocation suffices
+ * for repeated launches of the SAME descriptor; a scratch buffer that is reused with
+ * another M/N/K must be zeroed again first (partial sums of the old shape may lie where
+ * the new shape keeps control words).  Passing workspace = NULL to frisk_b200_gemm uses
+ * scratch owned by the context, which does this bookkeeping itself; such calls must not
+ * overlap on the GPU for one context. */
 size_t frisk_b200_gemm_workspace_bytes(const frisk_b200_gemm_desc* desc);
 /* Replaces the launch of the kernel the reference would have generated for a
  * `frisk.gemm` (benchmark/layout/execution/run_execution.py:84, load_cubin.py:18). */

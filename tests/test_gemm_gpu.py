@@ -125,7 +125,9 @@ def test_tc_config_4096_nt(ctx):
     assert np.array_equal(got.view(np.uint16), again.view(np.uint16))
     a2 = (a.astype(np.float32) * 2).astype(np.float16)
     doubled, _ = run_gemm(ctx, a2, b, "fp16", "fp16", M, N, K, False, True)
-    assert np.array_equal(doubled, (got.astype(np.float32) * 2).astype(np.float16))
+    normal = np.abs(got.astype(np.float32)) >= 2.0 ** -13  # doubling is not exact across fp16 subnormals
+    assert normal.mean() > 0.99
+    assert np.array_equal(doubled[normal], (got.astype(np.float32) * 2).astype(np.float16)[normal])
     # secondary cross-check of every element against the vendor GEMM (not authoritative)
     ta_, tb_ = to_device(a, "fp16"), to_device(b, "fp16")
     lib = (ta_.float() @ tb_.float().T).cpu().numpy()
@@ -174,7 +176,7 @@ def test_gemm_host_entry(ctx):
 
 def test_contract_errors_before_launch(ctx):
     import torch
-    a = torch.zeros(64, 64, dtype=torch.float16, device="cuda")
+    a = torch.zeros(128, 64, dtype=torch.float16, device="cuda")  # room for a shifted 64x64 view
     desc = capi.gemm_desc(64, 64, 64, "fp16", "fp16", False, True)
     with pytest.raises(ValueError, match="overlaps"):
         ctx.gemm(desc, a.data_ptr(), a.data_ptr(), a.data_ptr())
