@@ -25,6 +25,7 @@ EXPORTS = (
     "frisk_b200_gemm_select", "frisk_b200_gemm_workspace_bytes", "frisk_b200_gemm", "frisk_b200_gemm_host",
     "frisk_b200_attention_validate", "frisk_b200_attention_workspace_bytes", "frisk_b200_attention_fwd",
     "frisk_b200_attention_fwd_host", "frisk_b200_convert_f32", "frisk_b200_check",
+    "frisk_b200_gemm_skinny_static",
 )
 
 
@@ -78,6 +79,7 @@ def load():
         "frisk_b200_attention_fwd_host": (ctypes.c_int, [vp, ad, vp, vp, vp, vp]),
         "frisk_b200_convert_f32": (ctypes.c_int, [vp, vp, vp, i64, i32, vp]),
         "frisk_b200_check": (ctypes.c_int, [vp, vp]),
+        "frisk_b200_gemm_skinny_static": (ctypes.c_int, [ctypes.c_int, gd, vp, vp, vp, vp]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(lib, name)

@@ -284,3 +284,61 @@ int launch_gemm_skinny(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc& d, const
 }
 
 }  // namespace fb
+
+// ---------------------------------------------------------------------------------------
+// Entry point that allocates nothing.
+//
+// Some users of this library are not allowed to allocate device memory at the moment they
+// need a decode-shape GEMM: a serving process whose memory manager claimed all of HBM at
+// start-up (a later cudaMalloc simply fails), or a latency-critical loop that cannot accept
+// the device-wide synchronisation that cudaMalloc / cudaFree imply.  For them the split-K
+// scratch of the skinny kernel lives in a fixed array in the library's device image.  It is
+// part of the image, so every GPU that loads the library carries these bytes until the
+// process exits; the size is therefore kept modest and larger problems are refused.
+namespace fb {
+namespace {
+
+constexpr size_t kStaticScratchBytes = 8u << 20;  // 8 MiB: the 16 x 28672 x 8192 decode GEMM needs 5.3 MiB
+constexpr int kMaxDevices = 64;
+
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+// In host code `g_static_scratch` is only a handle for the symbol, not a device address, so
+// the address each device gave the array is looked up once (with that device current) and
+// kept here.
+std::mutex g_static_mu;
+void* g_static_ptr[kMaxDevices] = {};
+
+int static_scratch_for(int device, void** out) {
+  if (device < 0 || device >= kMaxDevices) return FRISK_B200_E_ARG;
+  std::lock_guard<std::mutex> lock(g_static_mu);
+  if (!g_static_ptr[device]) {
+    void* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&p, g_static_scratch);
+    if (e != cudaSuccess || !p) return FRISK_B200_E_CUDA;
+    g_static_ptr[device] = p;
+  }
+  *out = g_static_ptr[device];
+  return 0;
+}
+
+}  // namespace
+}  // namespace fb
+
+extern "C" int frisk_b200_gemm_skinny_static(int device, const frisk_b200_gemm_desc* desc, const void* A,
+                                             const void* B, void* C, void* stream) {
+  using namespace fb;
+  if (!desc || !A || !B || !C) return FRISK_B200_E_ARG;
+  int rc = frisk_b200_gemm_validate(desc);
+  if (rc) return rc;
+  if (!skinny_supported(*desc)) return FRISK_B200_E_UNSUPPORTED;
+  if (skinny_workspace_bytes(*desc) > kStaticScratchBytes) return FRISK_B200_E_TOO_LARGE;
+  if (cudaSetDevice(device) != cudaSuccess) return FRISK_B200_E_CUDA;
+  void* scratch = nullptr;
+  if ((rc = static_scratch_for(device, &scratch))) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // The array keeps whatever the previous call (possibly of another shape) left in it:
+  // the counters and tickets at its start must be zero before the kernel runs.
+  if (cudaMemsetAsync(scratch, 0, skinny_control_bytes(*desc), s) != cudaSuccess) return FRISK_B200_E_CUDA;
+  return launch_gemm_skinny(nullptr, *desc, A, B, C, scratch, kStaticScratchBytes, s);
+}

@@ -142,6 +142,23 @@ int frisk_b200_gemm(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc* desc, const
  * C back and returns when C is valid.  The end-to-end path of the benchmark. */
 int frisk_b200_gemm_host(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc* desc, const void* A,
                          const void* B, void* C);
+/* The decode-shape (M <= 16, trans_a = 0, trans_b = 1, fp16/bf16) GEMM for callers that must
+ * not allocate device memory when they call: processes whose memory manager reserved all of
+ * HBM at start-up, so a cudaMalloc made now would fail, and latency-critical loops that cannot
+ * take the device-wide synchronisation of cudaMalloc / cudaFree.  It has no counterpart in the
+ * reference (whose kernels need no scratch); it needs no context either, because creating one
+ * allocates.  The kernel's split-K scratch is a fixed 8 MiB array inside the library's device
+ * image (every GPU that loads the library holds those 8 MiB until the process exits).
+ *  - Problems whose scratch (frisk_b200_gemm_workspace_bytes) exceeds 8 MiB are refused with
+ *    FRISK_B200_E_TOO_LARGE; nothing is launched.
+ *  - The first call on a device looks up that device's address of the array; make that first
+ *    call outside any stream capture.  No call allocates or frees anything.
+ *  - All calls on a device share the one array.  Each call clears the control words it needs
+ *    on `stream` before its kernel, but two calls that overlap on the GPU (different streams)
+ *    race on it: serialise them.
+ * Results are bit-identical to frisk_b200_gemm with FRISK_B200_ALGO_SKINNY. */
+int frisk_b200_gemm_skinny_static(int device, const frisk_b200_gemm_desc* desc, const void* A,
+                                  const void* B, void* C, void* stream);
 
 /* ---- attention forward -----------------------------------------------------------------
  * Replaces the launch of `frisk_execution` for the attention graph
