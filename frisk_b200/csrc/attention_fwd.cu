@@ -10,10 +10,10 @@
 //
 //   * one CTA owns TWO 128-row query tiles of one (batch, head) and streams 128-key K/V tiles
 //     through a 2-stage TMA ring (K and V have separate full/empty mbarriers);
-//   * warp 0 is the TMA producer, warp 1 issues every tcgen05.mma: S_q = Q_q.K^T (SS form,
+//   * warp 8 is the TMA producer, warp 9 issues every tcgen05.mma: S_q = Q_q.K^T (SS form,
 //     both operands K-major, 128-byte swizzle) into tensor memory and O_q += P_q.V (P read
 //     from tensor memory, V as an MN-major shared-memory operand);
-//   * warps 2-5 and 6-9 are the two softmax groups: thread r owns row r of its query tile
+//   * warps 0-3 and 4-7 are the two softmax groups: thread r owns row r of its query tile
 //     (TMEM lane r), so row max / row sum need no shuffles.  The two groups alternate, so
 //     the tensor core works on one tile's MMAs while the other group exponentiates;
 //   * the running maximum is applied lazily: O is rescaled in tensor memory only when the
@@ -33,7 +33,8 @@ namespace {
 constexpr int BM = 128;        // query rows per tile (two tiles per CTA)
 constexpr int BN = 128;        // keys per K/V tile
 constexpr int kStagesKV = 2;
-constexpr int kThreads = 320;  // TMA warp, MMA warp, 2 x 4 softmax warps
+constexpr int kThreads = 320;  // warps 0-3, 4-7: softmax groups; warp 8: TMA; warp 9: MMA
+constexpr int kWarpTma = 8, kWarpMma = 9;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
 
 enum : unsigned { ST_ATTN_S = 0x201, ST_ATTN_P = 0x202, ST_ATTN_O = 0x203, ST_ATTN_KV = 0x204, ST_ATTN_Q = 0x205 };
@@ -58,8 +59,30 @@ struct AttnParams {
 
 __device__ __forceinline__ float ex2f(float x) {
   float y;
-  asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+
+__device__ __forceinline__ float max3f(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+// packed fp32 pairs (one instruction for two lanes of the row)
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
+  float2 d;
+  asm("fma.rn.ftz.f32x2 %0, %1, %2, %3;"
+      : "=l"(*reinterpret_cast<unsigned long long*>(&d))
+      : "l"(*reinterpret_cast<unsigned long long*>(&a)), "l"(*reinterpret_cast<unsigned long long*>(&b)),
+        "l"(*reinterpret_cast<unsigned long long*>(&c)));
+  return d;
+}
+__device__ __forceinline__ float2 add2(float2 a, float2 b) {
+  float2 d;
+  asm("add.rn.ftz.f32x2 %0, %1, %2;"
+      : "=l"(*reinterpret_cast<unsigned long long*>(&d))
+      : "l"(*reinterpret_cast<unsigned long long*>(&a)), "l"(*reinterpret_cast<unsigned long long*>(&b)));
+  return d;
 }
 
 template <bool BF16>
@@ -128,7 +151,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     tma_prefetch_desc(&tmap_k);
     tma_prefetch_desc(&tmap_v);
   }
-  if (warp == 1) {
+  if (warp == kWarpMma) {
     tmem_alloc(tmem_slot, 512);
     tmem_relinquish();
   }
@@ -137,7 +160,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 0) {
+  if (warp == kWarpTma) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0 && n_max > 0) {
       mbar_expect_tx(q_full, 2 * L::kTileBytes);
@@ -167,7 +190,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
       }
     }
-  } else if (warp == 1) {
+  } else if (warp == kWarpMma) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0 && n_max > 0) {
       constexpr uint32_t idesc_s = umma_idesc_f16(BM, BN, BF16, false, false);
@@ -244,9 +267,9 @@ __global__ void __launch_bounds__(kThreads, 1)
         umma_commit(&v_empty[j % kStagesKV]);
       }
     }
-  } else {
+  } else if (warp < 8) {
     // ------------------------------------------------------------------ softmax groups
-    const int q = (warp - 2) >> 2;   // query tile of this group
+    const int q = warp >> 2;         // query tile of this group
     const int quad = warp & 3;       // TMEM lane quadrant this warp may touch
     const int row = quad * 32 + lane;
     const int n_tiles = nq[q];
@@ -267,28 +290,34 @@ __global__ void __launch_bounds__(kThreads, 1)
         break;
       }
       tc_fence_after_sync();
-      uint32_t sr[128];
+      uint32_t sr[4][32];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) tmem_ld_32x32b_x32(t_s + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&sr[c * 32]));
+      for (int c = 0; c < 4; ++c) tmem_ld_32x32b_x32(t_s + c * 32, sr[c]);
       tmem_ld_wait();
 
       const int n0 = j * BN;
       const bool needs_mask = (n0 + BN > p.S_kv) || (p.causal && (n0 + BN - 1 > m_tile + off));
-      float mx = -INFINITY;
       if (needs_mask) {
         int limit = p.S_kv - 1;
         if (p.causal) limit = min(limit, g_row + off);
         limit -= n0;  // columns > limit are hidden
 #pragma unroll
-        for (int c = 0; c < 128; ++c) {
-          float s = (c > limit) ? -INFINITY : __uint_as_float(sr[c]);
-          sr[c] = __float_as_uint(s);
-          mx = fmaxf(mx, s);
-        }
-      } else {
+        for (int c = 0; c < 4; ++c)
 #pragma unroll
-        for (int c = 0; c < 128; ++c) mx = fmaxf(mx, __uint_as_float(sr[c]));
+          for (int i = 0; i < 32; ++i)
+            if (c * 32 + i > limit) sr[c][i] = 0xff800000u;  // -inf
       }
+      // row maximum: four independent chains of three-input max
+      float mxc[4];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        mxc[c] = max3f(__uint_as_float(sr[c][0]), __uint_as_float(sr[c][1]), __uint_as_float(sr[c][2]));
+#pragma unroll
+        for (int i = 3; i + 1 < 32; i += 2)
+          mxc[c] = max3f(mxc[c], __uint_as_float(sr[c][i]), __uint_as_float(sr[c][i + 1]));
+        mxc[c] = fmaxf(mxc[c], __uint_as_float(sr[c][31]));
+      }
+      const float mx = max3f(mxc[0], mxc[1], fmaxf(mxc[2], mxc[3]));
       float m_new = fmaxf(m_ref, mx * p.scale_log2);
       if (m_new == -INFINITY) m_new = 0.f;  // a row that sees no key yet: keep everything finite
 
@@ -317,21 +346,25 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
       }
 
-      // P = 2^(s*scale_log2 - m_ref), row sum in fp32, P rounded to 16 bits for the MMA
-      const float neg_m = -m_ref;
-      float sum0 = 0.f, sum1 = 0.f;
-      uint32_t pk[64];
+      // P = 2^(s*scale_log2 - m_ref) with packed fp32 FMAs, row sum in fp32 (two packed
+      // accumulators), P rounded to 16 bits and written back over S chunk by chunk
+      const float2 scale2 = make_float2(p.scale_log2, p.scale_log2);
+      const float2 negm2 = make_float2(-m_ref, -m_ref);
+      float2 sum_a = make_float2(0.f, 0.f), sum_b = make_float2(0.f, 0.f);
 #pragma unroll
-      for (int c = 0; c < 64; ++c) {
-        float p0 = ex2f(fmaf(__uint_as_float(sr[2 * c]), p.scale_log2, neg_m));
-        float p1 = ex2f(fmaf(__uint_as_float(sr[2 * c + 1]), p.scale_log2, neg_m));
-        sum0 += p0;
-        sum1 += p1;
-        pk[c] = pack16<BF16>(p0, p1);
+      for (int c = 0; c < 4; ++c) {
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          float2 x = fma2(make_float2(__uint_as_float(sr[c][2 * i]), __uint_as_float(sr[c][2 * i + 1])), scale2, negm2);
+          float2 e = make_float2(ex2f(x.x), ex2f(x.y));
+          if (i & 1) sum_b = add2(sum_b, e); else sum_a = add2(sum_a, e);
+          pk[i] = pack16<BF16>(e.x, e.y);
+        }
+        tmem_st_32x32b_x16(t_s + c * 16, pk);
       }
-      l_sum += sum0 + sum1;
-      tmem_st_32x32b_x32(t_s, *reinterpret_cast<uint32_t(*)[32]>(&pk[0]));
-      tmem_st_32x32b_x32(t_s + 32, *reinterpret_cast<uint32_t(*)[32]>(&pk[32]));
+      sum_a = add2(sum_a, sum_b);
+      l_sum += sum_a.x + sum_a.y;
       tmem_st_wait();
       tc_fence_before_sync();
       mbar_arrive(&p_ready[q]);
@@ -379,7 +412,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   }
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == 1) {
+  if (warp == kWarpMma) {
     __syncwarp();
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, 512);
