@@ -33,7 +33,8 @@ namespace {
 constexpr int BM = 128;        // query rows per tile (two tiles per CTA)
 constexpr int BN = 128;        // keys per K/V tile
 constexpr int kStagesKV = 2;
-constexpr int kThreads = 320;  // warps 0-3, 4-7: softmax groups; warp 8: TMA; warp 9: MMA
+constexpr int kThreads = 384;  // warps 0-3, 4-7: softmax groups; warp 8: TMA; warp 9: MMA; 10-11 idle
+constexpr int kRegsSoftmax = 208, kRegsOther = 72;  // per-thread register budgets after setmaxnreg
 constexpr int kWarpTma = 8, kWarpMma = 9;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
 
@@ -160,6 +161,9 @@ __global__ void __launch_bounds__(kThreads, 1)
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
+  // the TMA/MMA warpgroup hands registers to the two softmax warpgroups (a full row of S per thread)
+  if (warp >= 8) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsOther));
   if (warp == kWarpTma) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0 && n_max > 0) {
@@ -267,7 +271,9 @@ __global__ void __launch_bounds__(kThreads, 1)
         umma_commit(&v_empty[j % kStagesKV]);
       }
     }
-  } else if (warp < 8) {
+  }
+  } else {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsSoftmax));
     // ------------------------------------------------------------------ softmax groups
     const int q = warp >> 2;         // query tile of this group
     const int quad = warp & 3;       // TMEM lane quadrant this warp may touch

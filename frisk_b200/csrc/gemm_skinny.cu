@@ -8,7 +8,9 @@
 //   in shared memory (16 x K/S elements, rows padded by 64 bytes so that the fragment
 //   reads below are bank-conflict free).
 // * A warp owns one group of 8 weight rows at a time, taken from a per-split queue in the
-//   workspace (an atomic counter), so all warps stay busy to the end of the stream.
+//   workspace (an atomic counter), so all warps stay busy to the end of the stream; the
+//   loads of the next 256-wide k chunk (or of the next row group) are issued before the
+//   current chunk is multiplied.
 // * Each lane loads 16 bytes (8 consecutive k) of "its" weight row.  Because a dot product
 //   does not care about the order of k, those 8 values feed two m16n8k16 tensor-core MMAs
 //   directly as B fragments, with the matching 8 values of X rows g and g+8 as A
@@ -119,70 +121,109 @@ __global__ void __launch_bounds__(kThreads, 1)
   const unsigned char* xs_hi = xs_lo + (size_t)8 * pitch;
   const int Npad = ngroups * 8;
 
-  while (true) {
-    unsigned ng = 0;
-    if (lane == 0) ng = atomicAdd(&ctl[s], 1u);
-    ng = __shfl_sync(0xffffffffu, ng, 0);
-    if (ng >= (unsigned)ngroups) break;
-
-    const int n_row = min((int)ng * 8 + g, N - 1);
-    const T* wrow = W + (int64_t)n_row * ldw + kbeg + t * 8;
-    float acc0[4] = {0.f, 0.f, 0.f, 0.f}, acc1[4] = {0.f, 0.f, 0.f, 0.f};
-
-    for (int k0 = 0; k0 < klen; k0 += kChunkK) {
-      uint4 w[kUnroll];
+  auto grab = [&]() -> unsigned {
+    unsigned v = 0;
+    if (lane == 0) v = atomicAdd(&ctl[s], 1u);
+    return __shfl_sync(0xffffffffu, v, 0);
+  };
+  auto row_ptr = [&](unsigned group) -> const T* {
+    const int n_row = min((int)group * 8 + g, N - 1);
+    return W + (int64_t)n_row * ldw + kbeg + t * 8;
+  };
+  auto load_chunk = [&](uint4 (&w)[kUnroll], const T* wrow, int k0) {
 #pragma unroll
-      for (int u = 0; u < kUnroll; ++u) {
-        int kk = k0 + u * kStepK + t * 8;
-        w[u] = (kk < klen) ? ldg_stream(wrow + k0 + u * kStepK) : make_uint4(0, 0, 0, 0);
+    for (int u = 0; u < kUnroll; ++u) {
+      int kk = k0 + u * kStepK + t * 8;
+      w[u] = (kk < klen) ? ldg_stream(wrow + k0 + u * kStepK) : make_uint4(0, 0, 0, 0);
+    }
+  };
+
+  // Software pipeline over (row group, 256-wide k chunk) items: the weight loads of the next
+  // item -- which may belong to the next row group -- are in flight while the current
+  // item is multiplied, so a warp always has 8..16 16-byte loads outstanding.
+  unsigned ng = grab();
+  if (ng < (unsigned)ngroups) {
+    int k0 = 0;
+    const T* wrow = row_ptr(ng);
+    uint4 wc[kUnroll];
+    load_chunk(wc, wrow, k0);
+    float acc0[4] = {0.f, 0.f, 0.f, 0.f}, acc1[4] = {0.f, 0.f, 0.f, 0.f};
+    while (true) {
+      unsigned ng_n = ng;
+      int k0_n = k0 + kChunkK;
+      if (k0_n >= klen) {
+        ng_n = grab();
+        k0_n = 0;
       }
+      const bool have_next = ng_n < (unsigned)ngroups;
+      const T* wrow_n = have_next ? (k0_n == 0 ? row_ptr(ng_n) : wrow) : wrow;
+      uint4 wn[kUnroll];
+      if (have_next) load_chunk(wn, wrow_n, k0_n);
+
 #pragma unroll
       for (int u = 0; u < kUnroll; ++u) {
         size_t off = (size_t)(k0 + u * kStepK) * sizeof(T);
         uint4 xa = *reinterpret_cast<const uint4*>(xs_lo + off);
         uint4 xb = *reinterpret_cast<const uint4*>(xs_hi + off);
-        mma16816<T>(acc0, xa.x, xb.x, xa.y, xb.y, w[u].x, w[u].y);
-        mma16816<T>(acc1, xa.z, xb.z, xa.w, xb.w, w[u].z, w[u].w);
+        mma16816<T>(acc0, xa.x, xb.x, xa.y, xb.y, wc[u].x, wc[u].y);
+        mma16816<T>(acc1, xa.z, xb.z, xa.w, xb.w, wc[u].z, wc[u].w);
       }
-    }
-    float c[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) c[i] = acc0[i] + acc1[i];
 
-    const int col = (int)ng * 8 + 2 * t;  // output columns col, col+1 ; rows g and g+8
-    if (S > 1) {
-      float* p = partials + ((size_t)s * 16 + g) * Npad + col;
-      __stcg(reinterpret_cast<float2*>(p), make_float2(c[0], c[1]));
-      __stcg(reinterpret_cast<float2*>(p + (size_t)8 * Npad), make_float2(c[2], c[3]));
-      __threadfence();
-      __syncwarp();
-      unsigned ticket = 0;
-      if (lane == 0) ticket = atomicAdd(&tickets[ng], 1u);
-      ticket = __shfl_sync(0xffffffffu, ticket, 0);
-      if (ticket != (unsigned)(S - 1)) continue;
-      __threadfence();
-      c[0] = c[1] = c[2] = c[3] = 0.f;
-      for (int ss = 0; ss < S; ++ss) {
-        const float* q = partials + ((size_t)ss * 16 + g) * Npad + col;
-        float2 lo = __ldcg(reinterpret_cast<const float2*>(q));
-        float2 hi = __ldcg(reinterpret_cast<const float2*>(q + (size_t)8 * Npad));
-        c[0] += lo.x; c[1] += lo.y; c[2] += hi.x; c[3] += hi.y;
-      }
-      if (lane == 0) tickets[ng] = 0;
-    }
+      if (k0_n == 0) {  // the current row group is complete
+        float c[4];
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      int r = g + 8 * h;
-      if (r >= M) continue;
+        for (int i = 0; i < 4; ++i) {
+          c[i] = acc0[i] + acc1[i];
+          acc0[i] = 0.f;
+          acc1[i] = 0.f;
+        }
+        const int col = (int)ng * 8 + 2 * t;  // output columns col, col+1 ; rows g and g+8
+        bool write_out = true;
+        if (S > 1) {
+          float* pp = partials + ((size_t)s * 16 + g) * Npad + col;
+          __stcg(reinterpret_cast<float2*>(pp), make_float2(c[0], c[1]));
+          __stcg(reinterpret_cast<float2*>(pp + (size_t)8 * Npad), make_float2(c[2], c[3]));
+          __threadfence();
+          __syncwarp();
+          unsigned ticket = 0;
+          if (lane == 0) ticket = atomicAdd(&tickets[ng], 1u);
+          ticket = __shfl_sync(0xffffffffu, ticket, 0);
+          write_out = ticket == (unsigned)(S - 1);
+          if (write_out) {
+            __threadfence();
+            c[0] = c[1] = c[2] = c[3] = 0.f;
+            for (int ss = 0; ss < S; ++ss) {
+              const float* qq = partials + ((size_t)ss * 16 + g) * Npad + col;
+              float2 lo = __ldcg(reinterpret_cast<const float2*>(qq));
+              float2 hi = __ldcg(reinterpret_cast<const float2*>(qq + (size_t)8 * Npad));
+              c[0] += lo.x; c[1] += lo.y; c[2] += hi.x; c[3] += hi.y;
+            }
+            if (lane == 0) tickets[ng] = 0;
+          }
+        }
+        if (write_out) {
 #pragma unroll
-      for (int j = 0; j < 2; ++j) {
-        int cc = col + j;
-        if (cc >= N) continue;
-        TO* y = Y + (int64_t)r * ldy + cc;
-        float v = c[2 * h + j];
-        if (accumulate) v += to_f32<TO>(*y);
-        *y = from_f32<TO>(v);
+          for (int h = 0; h < 2; ++h) {
+            int r = g + 8 * h;
+            if (r >= M) continue;
+#pragma unroll
+            for (int jj = 0; jj < 2; ++jj) {
+              int cc = col + jj;
+              if (cc >= N) continue;
+              TO* y = Y + (int64_t)r * ldy + cc;
+              float v = c[2 * h + jj];
+              if (accumulate) v += to_f32<TO>(*y);
+              *y = from_f32<TO>(v);
+            }
+          }
+        }
       }
+      if (!have_next) break;
+      ng = ng_n;
+      k0 = k0_n;
+      wrow = wrow_n;
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) wc[u] = wn[u];
     }
   }
 

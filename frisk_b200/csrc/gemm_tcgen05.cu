@@ -18,6 +18,8 @@
 // (lib/Dialect/Frisk/Target/SM90/SM90GemmConstraints.cpp:121-138); TMA writes them directly.
 // No TMA load uses cluster multicast.
 #include "common.cuh"
+#include <cstdlib>
+
 #include "ptx.cuh"
 
 namespace fb {
@@ -30,6 +32,10 @@ constexpr int kStages = 4;
 constexpr int kThreads = 192;
 constexpr int kEpiWarp0 = 2;
 constexpr int kGroupM = 8;   // tile raster: columns of 8 M-tiles, for L2 reuse of B
+// k-blocks between an optional L2 prefetch and the shared-memory load.  Measured on B200 at
+// 4096^3: 0 (off) 1250 TFLOP/s, 2: 946, 4: 952, 16: 1016 -- the prefetches compete with the
+// loads for the TMA unit, so it stays off; FRISK_B200_GEMM_PREFETCH overrides for experiments.
+constexpr int kPrefetchAhead = 0;
 
 template <int BN>
 struct SmemLayout {
@@ -50,6 +56,28 @@ __device__ __forceinline__ TileCoord tile_coord(int t, int tiles_m, int tiles_n)
   int gsize = min(tiles_m - first_m, kGroupM);
   int r = t - group * per_group;
   return TileCoord{first_m + r % gsize, r / gsize};
+}
+
+// Work items: the first n_full items are whole 128xBN tiles; the tiles that would form a
+// partial last wave are cut into two 128x(BN/2) items each, so that the last wave takes half
+// as long (see the host side for when this pays).
+struct Item {
+  int m0, n0, bn;
+};
+template <int BN>
+__device__ __forceinline__ Item get_item(int idx, int n_full, int tiles_m, int tiles_n) {
+  int t = idx, half = -1;
+  if (idx >= n_full) {
+    t = n_full + ((idx - n_full) >> 1);
+    half = (idx - n_full) & 1;
+  }
+  TileCoord tc = tile_coord(t, tiles_m, tiles_n);
+  Item it{tc.m * BM, tc.n * BN, BN};
+  if (half >= 0) {
+    it.n0 += half * (BN / 2);
+    it.bn = BN / 2;
+  }
+  return it;
 }
 
 template <typename TO>
@@ -145,7 +173,7 @@ template <typename TO, int BN, bool BF16, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(kThreads, 1)
     gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                         TO* __restrict__ C, int M, int N, int K, int64_t ldc, int accumulate, int vec_c,
-                        unsigned* __restrict__ status) {
+                        int n_full, int n_items, int prefetch_ahead, unsigned* __restrict__ status) {
   using L = SmemLayout<BN>;
   extern __shared__ unsigned char smem_unaligned[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(
@@ -159,7 +187,6 @@ __global__ void __launch_bounds__(kThreads, 1)
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
-  const int num_tiles = tiles_m * tiles_n;
   const int num_kb = (K + BK - 1) / BK;
 
   if (threadIdx.x == 0) {
@@ -191,17 +218,33 @@ __global__ void __launch_bounds__(kThreads, 1)
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-        TileCoord tc = tile_coord(t, tiles_m, tiles_n);
-        const int m0 = tc.m * BM, n0 = tc.n * BN;
+      for (int t = blockIdx.x; t < n_items && ok; t += gridDim.x) {
+        const Item it = get_item<BN>(t, n_full, tiles_m, tiles_n);
+        const int m0 = it.m0, n0 = it.n0;
         for (int kb = 0; kb < num_kb; ++kb) {
+          // pull a k-block that is several ring depths ahead into L2, so that the ring itself
+          // only has to cover L2 latency
+          if (prefetch_ahead > 0 && kb + prefetch_ahead < num_kb) {
+            const int kp = (kb + prefetch_ahead) * BK;
+            if (A_MN) {
+#pragma unroll
+              for (int j = 0; j < BM / 64; ++j) tma_prefetch_l2_2d(&tmap_a, m0 + j * 64, kp);
+            } else {
+              tma_prefetch_l2_2d(&tmap_a, kp, m0);
+            }
+            if (B_MN) {
+              for (int j = 0; j < it.bn / 64; ++j) tma_prefetch_l2_2d(&tmap_b, n0 + j * 64, kp);
+            } else {
+              for (int j = 0; j < it.bn / 128; ++j) tma_prefetch_l2_2d(&tmap_b, kp, n0 + j * 128);
+            }
+          }
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, status, ST_TIMEOUT_EMPTY)) {
             ok = false;
             break;
           }
           unsigned char* sa = smem + stage * L::kStageBytes;
           unsigned char* sb = sa + L::kABytes;
-          mbar_expect_tx(&full_bar[stage], L::kStageBytes);
+          mbar_expect_tx(&full_bar[stage], L::kABytes + it.bn * (BK * 2));
           const int k0 = kb * BK;
           if (A_MN) {
 #pragma unroll
@@ -211,11 +254,12 @@ __global__ void __launch_bounds__(kThreads, 1)
             tma_load_2d(sa, &tmap_a, &full_bar[stage], k0, m0);
           }
           if (B_MN) {
-#pragma unroll
-            for (int j = 0; j < BN / 64; ++j)
+            for (int j = 0; j < it.bn / 64; ++j)
               tma_load_2d(sb + j * (BK * 128), &tmap_b, &full_bar[stage], n0 + j * 64, k0);
           } else {
-            tma_load_2d(sb, &tmap_b, &full_bar[stage], k0, n0);
+            // boxes of 128 rows: stacked 8-row groups, the same image as one taller box
+            for (int j = 0; j < it.bn / 128; ++j)
+              tma_load_2d(sb + j * (128 * BK * 2), &tmap_b, &full_bar[stage], k0, n0 + j * 128);
           }
           if (++stage == kStages) {
             stage = 0;
@@ -227,13 +271,15 @@ __global__ void __launch_bounds__(kThreads, 1)
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      constexpr uint32_t idesc = umma_idesc_f16(BM, BN, BF16, A_MN, B_MN);
+      constexpr uint32_t idesc_full = umma_idesc_f16(BM, BN, BF16, A_MN, B_MN);
+      constexpr uint32_t idesc_half = umma_idesc_f16(BM, BN / 2, BF16, A_MN, B_MN);
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      for (int t = blockIdx.x; t < n_items && ok; t += gridDim.x) {
+        const uint32_t idesc = (t >= n_full) ? idesc_half : idesc_full;
         if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag, status, ST_TIMEOUT_ACC_EMPTY)) break;
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * BN;
@@ -272,15 +318,15 @@ __global__ void __launch_bounds__(kThreads, 1)
     const int quad = warp & 3;  // TMEM lanes [32*quad, 32*quad+32) are this warp's
     int acc = 0;
     uint32_t acc_phase = 0;
-    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
-      TileCoord tc = tile_coord(t, tiles_m, tiles_n);
-      const int m0 = tc.m * BM, n0 = tc.n * BN;
+    for (int t = blockIdx.x; t < n_items; t += gridDim.x) {
+      const Item it = get_item<BN>(t, n_full, tiles_m, tiles_n);
+      const int m0 = it.m0, n0 = it.n0;
       if (!mbar_wait(&acc_full[acc], acc_phase, abort_flag, status, ST_TIMEOUT_ACC_FULL)) break;
       tc_fence_after_sync();
       const int row = m0 + quad * 32 + lane;
       const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(quad * 32) << 16);
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int c = 0; c < it.bn / 32; ++c) {
         uint32_t v[32];
         tmem_ld_32x32b_x32(taddr + c * 32, v);
         tmem_ld_wait();
@@ -329,7 +375,7 @@ int launch_cfg(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc& d, const void* A
   if (B_MN)
     rc = encode_tmap_2d(&tb, d.dtype_ab, B, (uint64_t)g.N, (uint64_t)g.K, (uint64_t)g.ldb * 2, 64, BK, true);
   else
-    rc = encode_tmap_2d(&tb, d.dtype_ab, B, (uint64_t)g.K, (uint64_t)g.N, (uint64_t)g.ldb * 2, BK, BN, true);
+    rc = encode_tmap_2d(&tb, d.dtype_ab, B, (uint64_t)g.K, (uint64_t)g.N, (uint64_t)g.ldb * 2, BK, 128, true);
   if (rc) { if (ctx) ctx->last_cuda = rc; return FRISK_B200_E_CUDA; }
 
   auto kern = gemm_tcgen05_kernel<TO, BN, BF16, A_MN, B_MN>;
@@ -337,9 +383,21 @@ int launch_cfg(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc& d, const void* A
   FB_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
   int tiles = (int)(((g.M + BM - 1) / BM) * ((g.N + BN - 1) / BN));
   int grid = tiles < ctx->num_sms ? tiles : ctx->num_sms;
+  // A partial last wave of at most grid/2 tiles runs as twice as many half-width items: the
+  // wave then costs half a tile time instead of a whole one.
+  int rem = tiles % grid;
+  int n_full = tiles, n_items = tiles;
+  if (tiles > grid && rem > 0 && 2 * rem <= grid) {
+    n_full = tiles - rem;
+    n_items = n_full + 2 * rem;
+  }
+  int prefetch = kPrefetchAhead;
+  if (const char* e = getenv("FRISK_B200_GEMM_PREFETCH")) prefetch = atoi(e);
+  if (const char* e = getenv("FRISK_B200_GEMM_NO_TAIL_SPLIT"))
+    if (e[0] == '1') n_full = n_items = tiles;
   int vec_c = aligned16(C) && (g.ldc * sizeof(TO)) % 16 == 0;
   kern<<<grid, kThreads, L::kTotal, s>>>(ta, tb, static_cast<TO*>(C), (int)g.M, (int)g.N, (int)g.K, g.ldc,
-                                         d.clear_accum ? 0 : 1, vec_c, ctx->d_status);
+                                         d.clear_accum ? 0 : 1, vec_c, n_full, n_items, prefetch, ctx->d_status);
   FB_CUDA(ctx, cudaGetLastError());
   return 0;
 }

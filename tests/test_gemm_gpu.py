@@ -107,6 +107,14 @@ def test_tc_many_tiles_persistent(ctx):
     check(ctx, 2048, 4096, 256, "bf16", "bf16", False, True, 28, algo=capi.ALGO_TCGEN05, dist="normal_rsqrt_k")
 
 
+@pytest.mark.parametrize("tb", [True, False])
+def test_tc_tail_wave_of_half_tiles(ctx, tb):
+    # 16 x 10 = 160 tiles on 148 SMs: the 12 tiles of the last wave run as 24 half-width items
+    check(ctx, 2048, 2560, 192, "bf16", "bf16", False, tb, 29, algo=capi.ALGO_TCGEN05, dist="normal_rsqrt_k")
+    # ragged N: the second half of the last tile column lies wholly outside the matrix
+    check(ctx, 2048, 2400, 64, "fp16", "fp32", False, tb, 30, algo=capi.ALGO_TCGEN05, dist="normal_rsqrt_k")
+
+
 def test_tc_config_4096_nt(ctx):
     """Full benchmark size: rows sampled against the fp64 oracle, the whole matrix against
     size-independent properties (deterministic rerun; C(2A) = 2C exactly in fp16)."""
