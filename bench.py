@@ -229,7 +229,7 @@ def run_ours(args):
             "config": {"workload": "fp16 GEMM M=N=K=4096 per GPU, A row-major, B column-major (NT), "
                                    "fp32 accumulate, fp16 out",
                        "sharding": "independent M-row shards, one 4096x4096x4096 product per GPU, no collective",
-                       "kernel": "gemm_tcgen05 (tcgen05.mma 128x256x16, TMEM accumulators, TMA 4-stage ring)",
+                       "kernel": "gemm_tcgen05_2cta (tcgen05.mma cta_group::2 256x256x16 per CTA pair, TMEM accumulators, TMA 6-stage ring, no multicast)",
                        "l2": f"inputs rotate through {len(sets)} operand sets "
                              f"({len(sets) * 3 * M * N * 2 / 2**20:.0f} MiB > 126 MiB L2)",
                        "pct_of_nominal_dense_peak": round(100 * value / world / NOMINAL_TENSOR_TFLOPS, 2)},

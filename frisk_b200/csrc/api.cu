@@ -261,7 +261,7 @@ int frisk_b200_gemm_validate(const frisk_b200_gemm_desc* d) {
   GemmDims g = resolve_dims(*d);
   int64_t a_cols = d->trans_a ? g.M : g.K, b_cols = d->trans_b ? g.K : g.N;
   if (g.lda < a_cols || g.ldb < b_cols || g.ldc < g.N) return FRISK_B200_E_GEMM_SHAPE;
-  if (d->algo < FRISK_B200_ALGO_AUTO || d->algo > FRISK_B200_ALGO_SKINNY) return FRISK_B200_E_ARG;
+  if (d->algo < FRISK_B200_ALGO_AUTO || d->algo > FRISK_B200_ALGO_TCGEN05_PAIR) return FRISK_B200_E_ARG;
   return 0;
 }
 
@@ -311,11 +311,12 @@ int frisk_b200_gemm_select(const frisk_b200_gemm_desc* d) {
   if (d->algo != FRISK_B200_ALGO_AUTO) {
     if (d->algo == FRISK_B200_ALGO_SIMT_F32) return d->dtype_ab == FRISK_B200_F32 ? d->algo : FRISK_B200_E_UNSUPPORTED;
     if (d->algo == FRISK_B200_ALGO_SKINNY) return skinny_supported(*d) ? d->algo : FRISK_B200_E_UNSUPPORTED;
-    if (d->algo == FRISK_B200_ALGO_TCGEN05) return tcgen05_supported(*d) ? d->algo : FRISK_B200_E_UNSUPPORTED;
+    if (d->algo == FRISK_B200_ALGO_TCGEN05 || d->algo == FRISK_B200_ALGO_TCGEN05_PAIR)
+      return tcgen05_supported(*d) ? d->algo : FRISK_B200_E_UNSUPPORTED;
   }
   if (d->dtype_ab == FRISK_B200_F32) return FRISK_B200_ALGO_SIMT_F32;
   if (skinny_supported(*d)) return FRISK_B200_ALGO_SKINNY;
-  if (tcgen05_supported(*d)) return FRISK_B200_ALGO_TCGEN05;
+  if (tcgen05_supported(*d)) return tcgen05_2cta_preferred(*d) ? FRISK_B200_ALGO_TCGEN05_PAIR : FRISK_B200_ALGO_TCGEN05;
   return FRISK_B200_E_ALIGN;  // 16-bit operands whose pitch is not a multiple of 16 bytes
 }
 
@@ -353,6 +354,8 @@ int frisk_b200_gemm(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc* d, const vo
     }
     case FRISK_B200_ALGO_TCGEN05:
       return launch_gemm_tcgen05(ctx, *d, A, B, C, s);
+    case FRISK_B200_ALGO_TCGEN05_PAIR:
+      return launch_gemm_tcgen05_2cta(ctx, *d, A, B, C, s);
   }
   return FRISK_B200_E_UNSUPPORTED;
 }
@@ -385,6 +388,9 @@ int frisk_b200_gemm_host(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc* d, con
     case FRISK_B200_ALGO_SKINNY:
       rc = launch_gemm_skinny(ctx, *d, ctx->stage[0].ptr, ctx->stage[1].ptr, ctx->stage[2].ptr, ctx->stage[3].ptr,
                               ctx->stage[3].bytes, s);
+      break;
+    case FRISK_B200_ALGO_TCGEN05_PAIR:
+      rc = launch_gemm_tcgen05_2cta(ctx, *d, ctx->stage[0].ptr, ctx->stage[1].ptr, ctx->stage[2].ptr, s);
       break;
     default:
       rc = launch_gemm_tcgen05(ctx, *d, ctx->stage[0].ptr, ctx->stage[1].ptr, ctx->stage[2].ptr, s);

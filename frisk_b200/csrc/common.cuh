@@ -86,6 +86,10 @@ bool tcgen05_supported(const frisk_b200_gemm_desc& d);
 int launch_gemm_tcgen05(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc& d, const void* A, const void* B,
                         void* C, cudaStream_t s);
 
+bool tcgen05_2cta_preferred(const frisk_b200_gemm_desc& d);
+int launch_gemm_tcgen05_2cta(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc& d, const void* A, const void* B,
+                             void* C, cudaStream_t s);
+
 int launch_attention_fwd(frisk_b200_ctx* ctx, const frisk_b200_attn_desc& d, const void* Q, const void* K,
                          const void* V, void* O, cudaStream_t s);
 

@@ -102,7 +102,7 @@ class SplitKGemm:
             self.ev_gemm = [torch.cuda.Event() for _ in range(plan.panels)]
             self.ev_comm = [torch.cuda.Event() for _ in range(plan.panels)]
             self.desc = capi.gemm_desc(plan.panel_rows, plan.N, plan.k_local, dtype, "fp32", False, True,
-                                       clear_accum=True, algo=capi.ALGO_TCGEN05)
+                                       clear_accum=True, algo=capi.ALGO_AUTO)
 
     def _gemm(self, a_panel, b, c, stream):
         if self._gemm_fn is not None:

@@ -37,8 +37,9 @@ enum { FRISK_B200_F32 = 0, FRISK_B200_F16 = 1, FRISK_B200_BF16 = 2 };
 enum {
   FRISK_B200_ALGO_AUTO = 0,
   FRISK_B200_ALGO_SIMT_F32 = 1, /* fp32 CUDA-core GEMM                                   */
-  FRISK_B200_ALGO_TCGEN05 = 2,  /* fp16/bf16 tcgen05 + TMEM + TMA ring                   */
-  FRISK_B200_ALGO_SKINNY = 3    /* M<=16 weight-streaming GEMM, split-K across CTAs      */
+  FRISK_B200_ALGO_TCGEN05 = 2,  /* fp16/bf16 tcgen05 + TMEM + TMA ring, one CTA per tile */
+  FRISK_B200_ALGO_SKINNY = 3,   /* M<=16 weight-streaming GEMM, split-K across CTAs      */
+  FRISK_B200_ALGO_TCGEN05_PAIR = 4 /* tcgen05 with CTA pairs (cta_group::2), 256x256 tiles */
 };
 
 /* error codes (negative: host-side contract checks) */

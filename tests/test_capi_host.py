@@ -61,8 +61,9 @@ def test_kernel_selection_and_workspace():
     lib = capi.load()
     sel = lambda d: lib.frisk_b200_gemm_select(d)  # noqa: E731
     assert sel(capi.gemm_desc(1024, 1024, 1024, "fp32")) == capi.ALGO_SIMT_F32
-    assert sel(capi.gemm_desc(4096, 4096, 4096, "fp16", trans_b=True)) == capi.ALGO_TCGEN05
-    assert sel(capi.gemm_desc(4096, 4096, 4096, "fp16")) == capi.ALGO_TCGEN05
+    assert sel(capi.gemm_desc(4096, 4096, 4096, "fp16", trans_b=True)) == capi.ALGO_TCGEN05_PAIR
+    assert sel(capi.gemm_desc(4096, 4096, 4096, "fp16")) == capi.ALGO_TCGEN05_PAIR
+    assert sel(capi.gemm_desc(1024, 1024, 4096, "fp16", trans_b=True)) == capi.ALGO_TCGEN05  # too few 256x256 tiles for pairs
     skinny = capi.gemm_desc(16, 28672, 8192, "bf16", trans_b=True)
     assert sel(skinny) == capi.ALGO_SKINNY
     assert lib.frisk_b200_gemm_workspace_bytes(skinny) > 0

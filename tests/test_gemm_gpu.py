@@ -12,6 +12,7 @@ from tests.util import Guarded, to_device, to_host
 
 pytestmark = pytest.mark.gpu
 TOL = {"fp32": 1e-3, "fp16": 5e-3, "bf16": 5e-3}
+TC_ALGOS = [capi.ALGO_TCGEN05, capi.ALGO_TCGEN05_PAIR]
 
 
 @pytest.fixture(scope="module")
@@ -76,35 +77,43 @@ def test_f32_tiny_and_odd_offsets(ctx):
 
 
 # ------------------------------------------------------------------ tcgen05
+@pytest.mark.parametrize("algo", TC_ALGOS)
 @pytest.mark.parametrize("dtype", ["fp16", "bf16"])
-def test_tc_single_tile(ctx, dtype):
-    # one 128x256 tile; 1, 2 and 5 k-blocks (ring wrap-around with 4 stages)
-    for K in (64, 128, 320):
-        check(ctx, 128, 256, K, dtype, dtype, False, True, 21, algo=capi.ALGO_TCGEN05, dist="normal_rsqrt_k")
+def test_tc_single_tile(ctx, dtype, algo):
+    # one tile; 1, 2, 5 and 7 k-blocks (ring wrap-around with 4 / 6 stages)
+    for K in (64, 128, 320, 448):
+        check(ctx, 128, 256, K, dtype, dtype, False, True, 21, algo=algo, dist="normal_rsqrt_k")
+        check(ctx, 256, 256, K, dtype, dtype, False, True, 21, algo=algo, dist="normal_rsqrt_k")
 
 
+@pytest.mark.parametrize("algo", TC_ALGOS)
 @pytest.mark.parametrize("dtype", ["fp16", "bf16"])
 @pytest.mark.parametrize("ta,tb", [(False, True), (False, False), (True, True), (True, False)])
-def test_tc_layouts(ctx, dtype, ta, tb):
-    check(ctx, 256, 512, 256, dtype, dtype, ta, tb, 22, algo=capi.ALGO_TCGEN05, dist="normal_rsqrt_k")
+def test_tc_layouts(ctx, dtype, ta, tb, algo):
+    check(ctx, 256, 512, 256, dtype, dtype, ta, tb, 22, algo=algo, dist="normal_rsqrt_k")
 
 
+@pytest.mark.parametrize("algo", TC_ALGOS)
 @pytest.mark.parametrize("ta,tb", [(False, True), (False, False), (True, True), (True, False)])
-def test_tc_ragged_edges(ctx, ta, tb):
+def test_tc_ragged_edges(ctx, ta, tb, algo):
     # M, N not multiples of the tile; K not a multiple of the k-block (TMA zero fill)
-    check(ctx, 200, 264, 72, "bf16", "bf16", ta, tb, 23, algo=capi.ALGO_TCGEN05, dist="normal_rsqrt_k")
-    check(ctx, 8, 8, 8, "fp16", "fp16", ta, tb, 24, algo=capi.ALGO_TCGEN05)
+    check(ctx, 200, 264, 72, "bf16", "bf16", ta, tb, 23, algo=algo, dist="normal_rsqrt_k")
+    check(ctx, 8, 8, 8, "fp16", "fp16", ta, tb, 24, algo=algo)
+    check(ctx, 300, 520, 200, "fp16", "fp16", ta, tb, 24, algo=algo, dist="normal_rsqrt_k")
 
 
-def test_tc_f32_output_and_accumulate(ctx):
-    check(ctx, 384, 256, 192, "fp16", "fp32", False, True, 25, algo=capi.ALGO_TCGEN05, dist="normal_rsqrt_k")
-    check(ctx, 384, 256, 192, "bf16", "fp32", False, True, 26, accumulate=True, algo=capi.ALGO_TCGEN05)
-    check(ctx, 130, 520, 136, "fp16", "fp16", False, True, 27, accumulate=True, algo=capi.ALGO_TCGEN05)
+@pytest.mark.parametrize("algo", TC_ALGOS)
+def test_tc_f32_output_and_accumulate(ctx, algo):
+    check(ctx, 384, 256, 192, "fp16", "fp32", False, True, 25, algo=algo, dist="normal_rsqrt_k")
+    check(ctx, 384, 256, 192, "bf16", "fp32", False, True, 26, accumulate=True, algo=algo)
+    check(ctx, 130, 520, 136, "fp16", "fp16", False, True, 27, accumulate=True, algo=algo)
 
 
-def test_tc_many_tiles_persistent(ctx):
-    # more tiles than SMs: every CTA walks several tiles and both accumulators
-    check(ctx, 2048, 4096, 256, "bf16", "bf16", False, True, 28, algo=capi.ALGO_TCGEN05, dist="normal_rsqrt_k")
+@pytest.mark.parametrize("algo", TC_ALGOS)
+def test_tc_many_tiles_persistent(ctx, algo):
+    # more tiles than SMs (or SM pairs): every CTA walks several tiles and both accumulators
+    check(ctx, 2048, 4096, 256, "bf16", "bf16", False, True, 28, algo=algo, dist="normal_rsqrt_k")
+    check(ctx, 4096, 4096, 128, "fp16", "fp16", False, False, 28, algo=algo, dist="normal_rsqrt_k")
 
 
 @pytest.mark.parametrize("tb", [True, False])
