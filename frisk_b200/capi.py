@@ -51,11 +51,12 @@ def load():
     global _lib
     if _lib is not None:
         return _lib
-    if not LIB_PATH.exists():
+    path = pathlib.Path(os.environ.get("FRISK_B200_LIB", LIB_PATH))  # override: try a differently built library
+    if not path.exists():
         raise RuntimeError(
-            f"{LIB_PATH} is missing: build it with `python -m frisk_b200.build` "
+            f"{path} is missing: build it with `python -m frisk_b200.build` "
             "(there is no CPU fallback for the GEMM / attention kernels)")
-    lib = ctypes.CDLL(os.fspath(LIB_PATH))
+    lib = ctypes.CDLL(os.fspath(path))
     vp, sz, i32, i64 = ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int32, ctypes.c_int64
     gd, ad = ctypes.POINTER(GemmDesc), ctypes.POINTER(AttnDesc)
     sig = {

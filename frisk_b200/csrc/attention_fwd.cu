@@ -27,6 +27,10 @@
 #include "common.cuh"
 #include "ptx.cuh"
 
+#ifndef FB_ATTN_EMULATE_EVERY
+#define FB_ATTN_EMULATE_EVERY 0
+#endif
+
 namespace fb {
 namespace {
 
@@ -37,6 +41,7 @@ constexpr int kThreads = 384;  // warps 0-3, 4-7: softmax groups; warp 8: TMA; w
 constexpr int kRegsSoftmax = 208, kRegsOther = 72;  // per-thread register budgets after setmaxnreg
 constexpr int kWarpTma = 8, kWarpMma = 9;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
+constexpr int kEmulateEvery = FB_ATTN_EMULATE_EVERY;  // 0 = never; 2 = every other pair of P values
 
 enum : unsigned { ST_ATTN_S = 0x201, ST_ATTN_P = 0x202, ST_ATTN_O = 0x203, ST_ATTN_KV = 0x204, ST_ATTN_Q = 0x205 };
 
@@ -86,6 +91,34 @@ __device__ __forceinline__ float2 add2(float2 a, float2 b) {
   return d;
 }
 
+__device__ __forceinline__ float2 add2_rm(float2 a, float2 b) {
+  float2 d;
+  asm("add.rm.ftz.f32x2 %0, %1, %2;"
+      : "=l"(*reinterpret_cast<unsigned long long*>(&d))
+      : "l"(*reinterpret_cast<unsigned long long*>(&a)), "l"(*reinterpret_cast<unsigned long long*>(&b)));
+  return d;
+}
+// 2^x for a pair of values on the FMA/ALU pipes instead of the special-function unit, which is
+// the scarcest resource of the softmax (16 ex2 per clock per SM against 128x128 scores per
+// tile).  x = n + f with n = floor(x) from a round-down add of 1.5*2^23, 2^f from a cubic
+// (max relative error 9e-5, far below the 2^-9 of the 16-bit P it is rounded to), and n is
+// added into the exponent field with integer arithmetic.
+__device__ __forceinline__ float2 ex2_emulated(float2 x) {
+  const float kMagic = 12582912.0f;  // 1.5 * 2^23
+  x.x = fmaxf(x.x, -127.0f);
+  x.y = fmaxf(x.y, -127.0f);
+  const float2 t = add2_rm(x, make_float2(kMagic, kMagic));
+  const float2 nf = add2(t, make_float2(-kMagic, -kMagic));
+  const float2 f = fma2(nf, make_float2(-1.0f, -1.0f), x);
+  float2 r = fma2(f, make_float2(0.077119089663028717f, 0.077119089663028717f),
+                  make_float2(0.227564394474029541f, 0.227564394474029541f));
+  r = fma2(r, f, make_float2(0.695146143436431885f, 0.695146143436431885f));
+  r = fma2(r, f, make_float2(1.0f, 1.0f));
+  r.x = __int_as_float(__float_as_int(r.x) + (__float_as_int(t.x) << 23));
+  r.y = __int_as_float(__float_as_int(r.y) + (__float_as_int(t.y) << 23));
+  return r;
+}
+
 template <bool BF16>
 __device__ __forceinline__ uint32_t pack16(float a, float b) {
   if (BF16) {
@@ -123,9 +156,10 @@ __global__ void __launch_bounds__(kThreads, 1)
   uint64_t* v_full = bars + 5;          // [2]
   uint64_t* v_empty = bars + 7;         // [2]
   uint64_t* s_full = bars + 9;          // [2] per query tile
-  uint64_t* p_ready = bars + 11;        // [2]
+  uint64_t* p_ready = bars + 11;        // [2] first half of P_q (keys 0-63) written
+  uint64_t* p_ready_hi = bars + 16;     // [2] second half written
   uint64_t* o_done = bars + 13;         // [2]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 20);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -144,6 +178,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       mbar_init(&v_empty[i], 1);
       mbar_init(&s_full[i], 1);
       mbar_init(&p_ready[i], 128);
+      mbar_init(&p_ready_hi[i], 128);
       mbar_init(&o_done[i], 1);
     }
     *abort_flag = 0;
@@ -203,27 +238,23 @@ __global__ void __launch_bounds__(kThreads, 1)
       bool ok = mbar_wait(q_full, 0, abort_flag, p.status, ST_ATTN_Q);
       tc_fence_after_sync();
 
+      // One thread issues every MMA, and a 128x128x16 MMA runs for only 64 clocks, so the
+      // instruction count per issue matters: descriptors are built once per tile and the k16
+      // slices only add a compile-time constant to the start-address field (low word).
+      const uint64_t dq0 = umma_desc_kmajor_sw128(sq), dq1 = umma_desc_kmajor_sw128(sq + L::kTileBytes);
+      const uint64_t dk0 = umma_desc_kmajor_sw128(sk), dk1 = umma_desc_kmajor_sw128(sk + L::kTileBytes);
+      const uint64_t dv0 = umma_desc_mnmajor_sw128(sv, kBoxBytes, 1024);
+      const uint64_t dv1 = umma_desc_mnmajor_sw128(sv + L::kTileBytes, kBoxBytes, 1024);
       auto issue_s = [&](int q, int stage) {
         const uint32_t d_tmem = tmem_base + q * 128;
+        const uint64_t da = q ? dq1 : dq0, db = stage ? dk1 : dk0;
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (kk / 4) * kBoxBytes + (kk % 4) * 32;
-          umma_f16_ss(d_tmem, umma_desc_kmajor_sw128(sq + q * L::kTileBytes + off),
-                      umma_desc_kmajor_sw128(sk + stage * L::kTileBytes + off), idesc_s, kk != 0);
+          const uint64_t off = static_cast<uint64_t>(((kk / 4) * kBoxBytes + (kk % 4) * 32) >> 4);
+          umma_f16_ss(d_tmem, da + off, db + off, idesc_s, kk != 0);
         }
         umma_commit(&s_full[q]);
       };
-      auto issue_pv = [&](int q, int stage, int j) {
-        const uint32_t d_tmem = tmem_base + 256 + q * 128;
-        const uint32_t a_tmem = tmem_base + q * 128;  // P_q: 8 columns per k16 slice
-#pragma unroll
-        for (int kk = 0; kk < BN / 16; ++kk)
-          umma_f16_ts(d_tmem, a_tmem + kk * 8,
-                      umma_desc_mnmajor_sw128(sv + stage * L::kTileBytes + kk * 2048, kBoxBytes, 1024), idesc_o,
-                      (j | kk) != 0);
-        umma_commit(&o_done[q]);
-      };
-
       int v_waited = 0;  // V tiles [0, v_waited) are known to have landed
       auto ensure_v = [&](int j) {
         while (ok && v_waited <= j) {
@@ -234,6 +265,26 @@ __global__ void __launch_bounds__(kThreads, 1)
         tc_fence_after_sync();
       };
 
+      // O_q += P_q(j) . V(j).  The softmax group publishes P in two halves (64 keys each), so
+      // the first four k16 slices start while the second half is still being exponentiated.
+      auto issue_pv = [&](int q, int stage, int j) {
+        const uint32_t d_tmem = tmem_base + 256 + q * 128;
+        const uint32_t a_tmem = tmem_base + q * 128;  // P_q: 8 columns per k16 slice
+        const uint64_t dv = stage ? dv1 : dv0;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          if (ok) ok = mbar_wait(half ? &p_ready_hi[q] : &p_ready[q], j & 1, abort_flag, p.status, ST_ATTN_P);
+          if (half == 0) ensure_v(j);
+          if (!ok) return;
+          tc_fence_after_sync();
+#pragma unroll
+          for (int kk = half * 4; kk < half * 4 + 4; ++kk)
+            umma_f16_ts(d_tmem, a_tmem + kk * 8, dv + static_cast<uint64_t>((kk * 2048) >> 4), idesc_o,
+                        (j | kk) != 0);
+        }
+        umma_commit(&o_done[q]);
+      };
+
       for (int j = 0; j < n_max && ok; ++j) {
         const int stage = j % kStagesKV;
         ok = mbar_wait(&k_full[stage], (j / kStagesKV) & 1, abort_flag, p.status, ST_ATTN_KV);
@@ -241,33 +292,20 @@ __global__ void __launch_bounds__(kThreads, 1)
         tc_fence_after_sync();
         if (j < nq[0]) issue_s(0, stage);
         if (j >= 1 && j - 1 < nq[1]) {  // O1 += P1(j-1) . V(j-1)
-          ok = mbar_wait(&p_ready[1], (j - 1) & 1, abort_flag, p.status, ST_ATTN_P);
-          ensure_v(j - 1);
-          if (!ok) break;
-          tc_fence_after_sync();
           issue_pv(1, (j - 1) % kStagesKV, j - 1);
+          if (!ok) break;
         }
         if (j >= 1) umma_commit(&v_empty[(j - 1) % kStagesKV]);  // both P.V of tile j-1 are issued
         if (j < nq[1]) issue_s(1, stage);
         umma_commit(&k_empty[stage]);  // both S of tile j are issued
         if (j < nq[0]) {               // O0 += P0(j) . V(j)
-          ok = mbar_wait(&p_ready[0], j & 1, abort_flag, p.status, ST_ATTN_P);
-          ensure_v(j);
-          if (!ok) break;
-          tc_fence_after_sync();
           issue_pv(0, stage, j);
+          if (!ok) break;
         }
       }
       if (ok && n_max >= 1) {
         const int j = n_max - 1;
-        if (j < nq[1]) {
-          ok = mbar_wait(&p_ready[1], j & 1, abort_flag, p.status, ST_ATTN_P);
-          ensure_v(j);
-          if (ok) {
-            tc_fence_after_sync();
-            issue_pv(1, j % kStagesKV, j);
-          }
-        }
+        if (j < nq[1]) issue_pv(1, j % kStagesKV, j);
         umma_commit(&v_empty[j % kStagesKV]);
       }
     }
@@ -363,17 +401,21 @@ __global__ void __launch_bounds__(kThreads, 1)
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
           float2 x = fma2(make_float2(__uint_as_float(sr[c][2 * i]), __uint_as_float(sr[c][2 * i + 1])), scale2, negm2);
-          float2 e = make_float2(ex2f(x.x), ex2f(x.y));
+          // every kEmulateEvery-th pair goes to the FMA pipes, the rest to the SFU
+          float2 e = (kEmulateEvery > 0 && (i % kEmulateEvery) == kEmulateEvery - 1) ? ex2_emulated(x)
+                                                                                  : make_float2(ex2f(x.x), ex2f(x.y));
           if (i & 1) sum_b = add2(sum_b, e); else sum_a = add2(sum_a, e);
           pk[i] = pack16<BF16>(e.x, e.y);
         }
         tmem_st_32x32b_x16(t_s + c * 16, pk);
+        if (c & 1) {  // a half of P (64 keys) is complete: let the MMA warp start on it
+          tmem_st_wait();
+          tc_fence_before_sync();
+          mbar_arrive(c == 1 ? &p_ready[q] : &p_ready_hi[q]);
+        }
       }
       sum_a = add2(sum_a, sum_b);
       l_sum += sum_a.x + sum_a.y;
-      tmem_st_wait();
-      tc_fence_before_sync();
-      mbar_arrive(&p_ready[q]);
     }
 
     // ---- epilogue: O / l
