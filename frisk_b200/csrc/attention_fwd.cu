@@ -492,6 +492,15 @@ int launch_cfg(frisk_b200_ctx* ctx, const frisk_b200_attn_desc& d, const void* Q
   if (p.total_ctas > INT32_MAX) return FRISK_B200_E_ATTN_SHAPE;
   auto kern = attention_fwd_kernel<BF16, D, OUT_F32>;
   using L = AttnSmem<D>;
+  // setmaxnreg.inc waits (without a bound) until the CTA's own register pool holds what it
+  // asks for: the registers the TMA/MMA warpgroup (128 threads) gives up must cover what the
+  // two softmax warpgroups (256 threads) take, or the kernel would never start.  Checked
+  // against the compiled register count before every launch.
+  cudaFuncAttributes fa;
+  FB_CUDA(ctx, cudaFuncGetAttributes(&fa, kern));
+  if (fa.numRegs < kRegsOther || fa.numRegs > kRegsSoftmax ||
+      (fa.numRegs - kRegsOther) * 128 < (kRegsSoftmax - fa.numRegs) * 256)
+    return FRISK_B200_E_UNSUPPORTED;
   FB_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
   kern<<<(unsigned)p.total_ctas, kThreads, L::kTotal, s>>>(tq, tk, tv, p);
   FB_CUDA(ctx, cudaGetLastError());
