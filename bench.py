@@ -47,61 +47,93 @@ def measured_peaks():
         return dict(FALLBACK_PEAKS), "fallback"
 
 
+# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures
+# summarised under profiles/ (one file per kernel and workload).
+NCU_TRAFFIC = {"gemm_tcgen05_f16_4096": 96546048, "gemm_skinny_bf16_16x28672x8192": 476130048}
+
+
 def ncu_traffic(key):
-    """DRAM bytes per launch from the committed ncu summary, or None."""
-    try:
-        with open(os.path.join(ROOT, "profiles", "ncu_traffic.json")) as f:
-            return json.load(f).get(key)
-    except Exception:
-        return None
+    return NCU_TRAFFIC.get(key)
 
 
 # ----------------------------------------------------------------------------- clocks
 class ClockSampler:
-    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
-    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
-              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    """Samples the SM clock and the throttle reasons through NVML (read-only queries) every few
+    milliseconds while the timed region runs; falls back to one nvidia-smi query if NVML is
+    not importable."""
 
     def __init__(self, gpu_index):
         self.gpu = gpu_index
-        self.rows = []
-        self.proc = None
+        self.samples = []
+        self.stop_flag = False
         self.thread = None
+        self.nvml = None
+        self.handle = None
 
     def start(self):
         try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", "-i", str(self.gpu), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            import pynvml
+            pynvml.nvmlInit()
+            self.nvml = pynvml
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+            index = self.gpu
+            if visible:
+                ids = [v.strip() for v in visible.split(",") if v.strip()]
+                if self.gpu < len(ids) and ids[self.gpu].isdigit():
+                    index = int(ids[self.gpu])
+            self.handle = pynvml.nvmlDeviceGetHandleByIndex(index)
         except Exception:
-            self.proc = None
+            self.nvml = None
             return
-        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread = threading.Thread(target=self._poll, daemon=True)
         self.thread.start()
 
-    def _read(self):
-        for line in self.proc.stdout:
-            self.rows.append((time.time(), [c.strip() for c in line.split(",")]))
+    def _poll(self):
+        n = self.nvml
+        while not self.stop_flag:
+            try:
+                sm = n.nvmlDeviceGetClockInfo(self.handle, n.NVML_CLOCK_SM)
+                reasons = n.nvmlDeviceGetCurrentClocksEventReasons(self.handle) if hasattr(
+                    n, "nvmlDeviceGetCurrentClocksEventReasons") else n.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle)
+                power = n.nvmlDeviceGetPowerUsage(self.handle) / 1000.0
+                self.samples.append((time.time(), sm, reasons, power))
+            except Exception:
+                pass
+            time.sleep(0.002)
 
     def stop(self, t0, t1):
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=2)
-        except Exception:
-            self.proc.kill()
-        rows = [r for t, r in self.rows if t0 - 0.05 <= t <= t1 + 0.15 and len(r) >= 9] or \
-               [r for _, r in self.rows if len(r) >= 9]
+        self.stop_flag = True
+        if self.nvml is None:
+            return self._smi_once()
+        if self.thread is not None:
+            self.thread.join(timeout=1)
+        n = self.nvml
+        rows = [s for s in self.samples if t0 <= s[0] <= t1] or self.samples[-3:]
         if not rows:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
-        sm = sorted(float(r[1]) for r in rows)
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = [n for i, n in enumerate(names) if any(r[5 + i].lower().startswith("active") for r in rows)]
-        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": float(rows[0][2]), "reasons": reasons,
-                "samples": len(rows), "power_w_max": max(float(r[3]) for r in rows)}
+        sm = sorted(r[1] for r in rows)
+        bits = 0
+        for r in rows:
+            bits |= r[2]
+        names = {"hw_slowdown": 0x8, "sw_power_cap": 0x4, "hw_thermal_slowdown": 0x40, "sw_thermal_slowdown": 0x20,
+                 "hw_power_brake_slowdown": 0x80}
+        reasons = [k for k, v in names.items() if bits & v]
+        try:
+            mx = n.nvmlDeviceGetMaxClockInfo(self.handle, n.NVML_CLOCK_SM)
+        except Exception:
+            mx = None
+        return {"sm_mhz": float(sm[len(sm) // 2]), "sm_min_mhz": float(sm[0]), "sm_max_mhz": float(mx) if mx else None,
+                "reasons": reasons, "samples": len(rows), "power_w_max": round(max(r[3] for r in rows), 1),
+                "source": "nvml, 2 ms polling inside the timed region"}
+
+    def _smi_once(self):
+        try:
+            out = subprocess.run(["nvidia-smi", "-i", str(self.gpu), "--query-gpu=clocks.sm,clocks.max.sm",
+                                  "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=10).stdout
+            a, b = [float(x) for x in out.strip().split(",")]
+            return {"sm_mhz": a, "sm_max_mhz": b, "reasons": [], "samples": 1, "source": "nvidia-smi after the run"}
+        except Exception:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no clock source"]}
 
 
 # ----------------------------------------------------------------------------- helpers
