@@ -1,5 +1,6 @@
 // C ABI of libfrisk_b200 (include/frisk_b200.h): context, host-side contract checks,
 // kernel selection, and the host-buffer entry points.
+#include <algorithm>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -211,6 +212,7 @@ int frisk_b200_ctx_create(frisk_b200_ctx** out, int device) {
   ctx->h_status[0] = 0;
   if ((e = cudaStreamCreateWithFlags(&ctx->host_stream, cudaStreamNonBlocking)) != cudaSuccess) return fail(e);
   if ((e = cudaStreamCreateWithFlags(&ctx->copy_stream, cudaStreamNonBlocking)) != cudaSuccess) return fail(e);
+  if ((e = cudaStreamCreateWithFlags(&ctx->out_stream, cudaStreamNonBlocking)) != cudaSuccess) return fail(e);
   for (auto& ev : ctx->ev)
     if ((e = cudaEventCreateWithFlags(&ev, cudaEventDisableTiming)) != cudaSuccess) return fail(e);
   *out = ctx;
@@ -229,6 +231,7 @@ int frisk_b200_ctx_destroy(frisk_b200_ctx* ctx) {
     if (ev) cudaEventDestroy(ev);
   if (ctx->host_stream) cudaStreamDestroy(ctx->host_stream);
   if (ctx->copy_stream) cudaStreamDestroy(ctx->copy_stream);
+  if (ctx->out_stream) cudaStreamDestroy(ctx->out_stream);
   delete ctx;
   return 0;
 }
@@ -323,6 +326,7 @@ int frisk_b200_gemm_select(const frisk_b200_gemm_desc* d) {
 size_t frisk_b200_gemm_workspace_bytes(const frisk_b200_gemm_desc* d) {
   int algo = frisk_b200_gemm_select(d);
   if (algo == FRISK_B200_ALGO_SKINNY) return skinny_workspace_bytes(*d);
+  if (algo == FRISK_B200_ALGO_TCGEN05_PAIR) return tcgen05_2cta_workspace_bytes(*d);
   return 0;
 }
 
@@ -354,8 +358,18 @@ int frisk_b200_gemm(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc* d, const vo
     }
     case FRISK_B200_ALGO_TCGEN05:
       return launch_gemm_tcgen05(ctx, *d, A, B, C, s);
-    case FRISK_B200_ALGO_TCGEN05_PAIR:
-      return launch_gemm_tcgen05_2cta(ctx, *d, A, B, C, s);
+    case FRISK_B200_ALGO_TCGEN05_PAIR: {
+      size_t need = tcgen05_2cta_workspace_bytes(*d);
+      if (need && !workspace) {
+        // library-owned scratch: zeroed when allocated, tickets are left at zero by every launch
+        std::lock_guard<std::mutex> lock(ctx->mu);
+        int rc = ensure_stage(ctx, 5, need, true);
+        if (rc) return rc;
+        workspace = ctx->stage[5].ptr;
+        workspace_bytes = ctx->stage[5].bytes;
+      }
+      return launch_gemm_tcgen05_2cta(ctx, *d, A, B, C, workspace, workspace_bytes, s);
+    }
   }
   return FRISK_B200_E_UNSUPPORTED;
 }
@@ -372,31 +386,64 @@ int frisk_b200_gemm_host(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc* d, con
   if ((rc = ensure_stage(ctx, 0, e.a, false))) return rc;
   if ((rc = ensure_stage(ctx, 1, e.b, false))) return rc;
   if ((rc = ensure_stage(ctx, 2, e.c, false))) return rc;
-  cudaStream_t s = ctx->host_stream, s2 = ctx->copy_stream;
+  cudaStream_t s = ctx->host_stream, s2 = ctx->copy_stream, s3 = ctx->out_stream;
   if (algo == FRISK_B200_ALGO_SKINNY && (rc = prepare_owned_skinny_ws(ctx, *d, s))) return rc;
-  // A and B travel on two streams so that both copy engines are used
-  FB_CUDA(ctx, cudaMemcpyAsync(ctx->stage[0].ptr, A, e.a, cudaMemcpyHostToDevice, s));
+  if (size_t need = (algo == FRISK_B200_ALGO_TCGEN05_PAIR ? tcgen05_2cta_workspace_bytes(*d) : 0))
+    if ((rc = ensure_stage(ctx, 5, need, true))) return rc;
+  GemmDims g = resolve_dims(*d);
+  const size_t es = dtype_size(d->dtype_ab), cs = dtype_size(d->dtype_c);
+
+  // Row panels of A and C travel while other panels are multiplied: H2D on one stream, the
+  // kernels on a second, D2H on a third, ordered by events (PCIe is full duplex, so the
+  // copy-out of panel p overlaps the copy-in of panel p+1).  Only when A's rows are
+  // contiguous in the buffer (trans_a = 0) and the problem is large enough to split.
+  int panels = 1;
+  if (!d->trans_a && algo != FRISK_B200_ALGO_SKINNY && g.M >= 1024 && e.a + e.c >= ((size_t)8 << 20)) panels = 4;
+  const int64_t rows_per = ((g.M + panels - 1) / panels + 255) / 256 * 256;
+  panels = (int)((g.M + rows_per - 1) / rows_per);
+
   FB_CUDA(ctx, cudaMemcpyAsync(ctx->stage[1].ptr, B, e.b, cudaMemcpyHostToDevice, s2));
-  if (!d->clear_accum) FB_CUDA(ctx, cudaMemcpyAsync(ctx->stage[2].ptr, C, e.c, cudaMemcpyHostToDevice, s2));
-  FB_CUDA(ctx, cudaEventRecord(ctx->ev[0], s2));
-  FB_CUDA(ctx, cudaStreamWaitEvent(s, ctx->ev[0], 0));
-  switch (algo) {
-    case FRISK_B200_ALGO_SIMT_F32:
-      rc = launch_gemm_simt_f32(ctx, *d, static_cast<const float*>(ctx->stage[0].ptr),
-                                static_cast<const float*>(ctx->stage[1].ptr), static_cast<float*>(ctx->stage[2].ptr), s);
-      break;
-    case FRISK_B200_ALGO_SKINNY:
-      rc = launch_gemm_skinny(ctx, *d, ctx->stage[0].ptr, ctx->stage[1].ptr, ctx->stage[2].ptr, ctx->stage[3].ptr,
-                              ctx->stage[3].bytes, s);
-      break;
-    case FRISK_B200_ALGO_TCGEN05_PAIR:
-      rc = launch_gemm_tcgen05_2cta(ctx, *d, ctx->stage[0].ptr, ctx->stage[1].ptr, ctx->stage[2].ptr, s);
-      break;
-    default:
-      rc = launch_gemm_tcgen05(ctx, *d, ctx->stage[0].ptr, ctx->stage[1].ptr, ctx->stage[2].ptr, s);
+  for (int p = 0; p < panels; ++p) {
+    const int64_t r0 = p * rows_per, rows = std::min<int64_t>(rows_per, g.M - r0);
+    frisk_b200_gemm_desc dp = *d;
+    dp.M = rows;
+    dp.lda = g.lda;
+    dp.ldb = g.ldb;
+    dp.ldc = g.ldc;
+    dp.algo = FRISK_B200_ALGO_AUTO;
+    const int algo_p = panels == 1 ? algo : frisk_b200_gemm_select(&dp);
+    if (algo_p < 0) return algo_p;
+    // with trans_a the single panel is the whole (K x M) buffer
+    const size_t a_off = d->trans_a ? 0 : (size_t)r0 * g.lda * es, a_bytes = panels == 1 ? e.a : operand_bytes(rows, g.K, g.lda, es);
+    const size_t c_off = (size_t)r0 * g.ldc * cs, c_bytes = operand_bytes(rows, g.N, g.ldc, cs);
+    unsigned char* dA = static_cast<unsigned char*>(ctx->stage[0].ptr) + a_off;
+    unsigned char* dC = static_cast<unsigned char*>(ctx->stage[2].ptr) + c_off;
+    FB_CUDA(ctx, cudaMemcpyAsync(dA, static_cast<const unsigned char*>(A) + a_off, a_bytes, cudaMemcpyHostToDevice, s2));
+    if (!d->clear_accum)
+      FB_CUDA(ctx, cudaMemcpyAsync(dC, static_cast<const unsigned char*>(C) + c_off, c_bytes, cudaMemcpyHostToDevice, s2));
+    FB_CUDA(ctx, cudaEventRecord(ctx->ev[2 * p], s2));
+    FB_CUDA(ctx, cudaStreamWaitEvent(s, ctx->ev[2 * p], 0));
+    switch (algo_p) {
+      case FRISK_B200_ALGO_SIMT_F32:
+        rc = launch_gemm_simt_f32(ctx, dp, reinterpret_cast<const float*>(dA), static_cast<const float*>(ctx->stage[1].ptr),
+                                  reinterpret_cast<float*>(dC), s);
+        break;
+      case FRISK_B200_ALGO_SKINNY:
+        rc = launch_gemm_skinny(ctx, dp, dA, ctx->stage[1].ptr, dC, ctx->stage[3].ptr, ctx->stage[3].bytes, s);
+        break;
+      case FRISK_B200_ALGO_TCGEN05_PAIR:
+        rc = launch_gemm_tcgen05_2cta(ctx, dp, dA, ctx->stage[1].ptr, dC, ctx->stage[5].ptr, ctx->stage[5].bytes, s);
+        break;
+      default:
+        rc = launch_gemm_tcgen05(ctx, dp, dA, ctx->stage[1].ptr, dC, s);
+    }
+    if (rc) return rc;
+    FB_CUDA(ctx, cudaEventRecord(ctx->ev[2 * p + 1], s));
+    FB_CUDA(ctx, cudaStreamWaitEvent(s3, ctx->ev[2 * p + 1], 0));
+    FB_CUDA(ctx, cudaMemcpyAsync(static_cast<unsigned char*>(C) + c_off, dC, c_bytes, cudaMemcpyDeviceToHost, s3));
   }
-  if (rc) return rc;
-  FB_CUDA(ctx, cudaMemcpyAsync(C, ctx->stage[2].ptr, e.c, cudaMemcpyDeviceToHost, s));
+  FB_CUDA(ctx, cudaEventRecord(ctx->ev[23], s3));
+  FB_CUDA(ctx, cudaStreamWaitEvent(s, ctx->ev[23], 0));
   FB_CUDA(ctx, cudaMemcpyAsync(ctx->h_status, ctx->d_status, sizeof(unsigned), cudaMemcpyDeviceToHost, s));
   FB_CUDA(ctx, cudaStreamSynchronize(s));
   ctx->last_status = (int)ctx->h_status[0];

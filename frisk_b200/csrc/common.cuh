@@ -35,10 +35,11 @@ struct frisk_b200_ctx {
   unsigned* d_status = nullptr;  // device status word (first failing wait records its code)
   unsigned* h_status = nullptr;  // pinned mirror
   // staging for the *_host entry points and library-owned workspace
-  fb::StagingBuffer stage[5];
+  fb::StagingBuffer stage[6];  // 0-2 A/B/C staging, 3 skinny scratch, 4 V staging, 5 GEMM tail scratch
   cudaStream_t host_stream = nullptr;
   cudaStream_t copy_stream = nullptr;
-  cudaEvent_t ev[8] = {};
+  cudaStream_t out_stream = nullptr;
+  cudaEvent_t ev[24] = {};
   std::mutex mu;
 };
 
@@ -87,8 +88,10 @@ int launch_gemm_tcgen05(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc& d, cons
                         void* C, cudaStream_t s);
 
 bool tcgen05_2cta_preferred(const frisk_b200_gemm_desc& d);
+// scratch for the K-split tail wave (0 when every tile runs whole); tickets at its start must be zero
+size_t tcgen05_2cta_workspace_bytes(const frisk_b200_gemm_desc& d);
 int launch_gemm_tcgen05_2cta(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc& d, const void* A, const void* B,
-                             void* C, cudaStream_t s);
+                             void* C, void* ws, size_t ws_bytes, cudaStream_t s);
 
 int launch_attention_fwd(frisk_b200_ctx* ctx, const frisk_b200_attn_desc& d, const void* Q, const void* K,
                          const void* V, void* O, cudaStream_t s);

@@ -35,6 +35,8 @@ constexpr int BK = 64;
 constexpr int UMMA_K = 16;
 constexpr int kStages2 = 6;
 constexpr int kThreads2 = 192;
+constexpr size_t kTicketBytes = 1024;
+constexpr int kPairsAssumed = kNumSMsDefault / 2;  // CTA pairs the tail plan (and its workspace size) is made for
 
 struct Smem2 {
   static constexpr int kABytes = BMC * BK * 2;
@@ -101,11 +103,26 @@ __device__ __forceinline__ void umma_commit_pair(uint64_t* bar, uint16_t mask) {
       : "memory");
 }
 
+// Work items.  Items [0, n_full) are whole tiles.  The tiles that would form a partial last
+// wave are each cut into two K halves (items n_full + 2*tail + half) that run side by side on
+// two CTA pairs; each half leaves its fp32 accumulator in the workspace and takes a ticket,
+// and the half that draws the second ticket adds the other half's values and writes C.
+// Nothing waits on another CTA.
+struct Item2 {
+  int tile, kb0, kb1, tail, half;
+};
+__device__ __forceinline__ Item2 get_item2(int i, int n_full, int num_kb) {
+  if (i < n_full) return Item2{i, 0, num_kb, -1, 0};
+  const int u = i - n_full, tail = u >> 1, half = u & 1, mid = num_kb >> 1;
+  return Item2{n_full + tail, half ? mid : 0, half ? num_kb : mid, tail, half};
+}
+
 template <typename TO, bool BF16, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(kThreads2, 1)
     gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                              TO* __restrict__ C, int M, int N, int K, int64_t ldc, int accumulate, int vec_c,
-                             unsigned* __restrict__ status) {
+                             int n_full, int n_items, float* __restrict__ partials,
+                             unsigned* __restrict__ tickets, unsigned* __restrict__ status) {
   using L = Smem2;
   extern __shared__ unsigned char smem_unaligned[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(
@@ -114,14 +131,15 @@ __global__ void __launch_bounds__(kThreads2, 1)
   uint64_t* empty_bar = full_bar + kStages2;
   uint64_t* acc_full = empty_bar + kStages2;  // [2]
   uint64_t* acc_empty = acc_full + 2;         // [2] (the leader's is the one that is used)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  uint64_t* epi_bar = acc_empty + 2;          // [1] the four epilogue warps of this CTA among themselves
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(epi_bar + 1);
   volatile uint32_t* abort_flag = tmem_slot + 1;
+  volatile uint32_t* epi_word = tmem_slot + 2;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();  // 0 = leader
   const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
   const int tiles_m = (M + BM2 - 1) / BM2, tiles_n = (N + BN2 - 1) / BN2;
-  const int num_tiles = tiles_m * tiles_n;
   const int num_kb = (K + BK - 1) / BK;
 
   if (threadIdx.x == 0) {
@@ -133,6 +151,7 @@ __global__ void __launch_bounds__(kThreads2, 1)
       mbar_init(&acc_full[i], 1);
       mbar_init(&acc_empty[i], 8);  // 4 epilogue warps of each CTA
     }
+    mbar_init(epi_bar, 128);
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmap_a);
@@ -154,11 +173,12 @@ __global__ void __launch_bounds__(kThreads2, 1)
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int t = pair; t < num_tiles && ok; t += num_pairs) {
-        TileCoord tc = tile_coord(t, tiles_m, tiles_n);
+      for (int t = pair; t < n_items && ok; t += num_pairs) {
+        const Item2 it = get_item2(t, n_full, num_kb);
+        TileCoord tc = tile_coord(it.tile, tiles_m, tiles_n);
         const int m0 = tc.m * BM2 + (int)rank * BMC;   // this CTA's rows of A (and of C)
         const int n0 = tc.n * BN2 + (int)rank * BNC;   // this CTA's half of the B tile
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = it.kb0; kb < it.kb1; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, status, ST_TIMEOUT_EMPTY)) {
             ok = false;
             break;
@@ -197,11 +217,12 @@ __global__ void __launch_bounds__(kThreads2, 1)
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (int t = pair; t < num_tiles && ok; t += num_pairs) {
+      for (int t = pair; t < n_items && ok; t += num_pairs) {
+        const Item2 it = get_item2(t, n_full, num_kb);
         if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag, status, ST_TIMEOUT_ACC_EMPTY)) break;
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * BN2;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = it.kb0; kb < it.kb1; ++kb) {
           if (!mbar_wait(&full_bar[stage], phase, abort_flag, status, ST_TIMEOUT_FULL)) {
             ok = false;
             break;
@@ -215,7 +236,7 @@ __global__ void __launch_bounds__(kThreads2, 1)
                                : umma_desc_kmajor_sw128(sa + k * (UMMA_K * 2));
             uint64_t db = B_MN ? umma_desc_mnmajor_sw128(sb + k * (UMMA_K * 128), BK * 128, 1024)
                                : umma_desc_kmajor_sw128(sb + k * (UMMA_K * 2));
-            umma_f16_ss_pair(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+            umma_f16_ss_pair(d_tmem, da, db, idesc, (kb > it.kb0 || k != 0) ? 1u : 0u);
           }
           umma_commit_pair(&empty_bar[stage], 3);  // both CTAs may refill this stage
           if (++stage == kStages2) {
@@ -237,21 +258,71 @@ __global__ void __launch_bounds__(kThreads2, 1)
     int acc = 0;
     uint32_t acc_phase = 0;
     const uint32_t leader_acc_empty0 = mapa_u32(&acc_empty[0], 0), leader_acc_empty1 = mapa_u32(&acc_empty[1], 0);
-    for (int t = pair; t < num_tiles; t += num_pairs) {
-      TileCoord tc = tile_coord(t, tiles_m, tiles_n);
+    uint32_t epi_phase = 0;
+    bool epi_ok = true;
+    // bounded meeting point of this CTA's 128 epilogue threads
+    auto epi_sync = [&]() {
+      mbar_arrive(epi_bar);
+      if (epi_ok) epi_ok = mbar_wait(epi_bar, epi_phase, abort_flag, status, ST_TIMEOUT_MISC);
+      epi_phase ^= 1;
+    };
+    for (int t = pair; t < n_items; t += num_pairs) {
+      const Item2 it = get_item2(t, n_full, num_kb);
+      TileCoord tc = tile_coord(it.tile, tiles_m, tiles_n);
       const int m0 = tc.m * BM2 + (int)rank * BMC, n0 = tc.n * BN2;
       if (!mbar_wait(&acc_full[acc], acc_phase, abort_flag, status, ST_TIMEOUT_ACC_FULL)) break;
       tc_fence_after_sync();
-      const int row = m0 + quad * 32 + lane;
+      const int row_local = quad * 32 + lane;
+      const int row = m0 + row_local;
       const uint32_t taddr = tmem_base + acc * BN2 + (static_cast<uint32_t>(quad * 32) << 16);
+      bool write_c = true;
+      const float4* other = nullptr;
+      if (it.tail >= 0) {
+        // leave this K half in the workspace, then see whether the other half is already there
+        // scratch layout per (tail tile, K half, CTA): [64 groups of 4 columns][128 rows] float4, so that
+        // the 32 lanes of a warp (32 consecutive rows) write and read consecutive 16-byte words
+        float4* mine = reinterpret_cast<float4*>(partials + (((size_t)it.tail * 2 + it.half) * 2 + rank) * (BMC * BN2)) + row_local;
+        other = reinterpret_cast<const float4*>(partials + (((size_t)it.tail * 2 + (it.half ^ 1)) * 2 + rank) * (BMC * BN2)) + row_local;
 #pragma unroll 1
-      for (int c = 0; c < BN2 / 32; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32b_x32(taddr + c * 32, v);
-        tmem_ld_wait();
-        const int col = n0 + c * 32;
-        if (row < M && col < N)
-          store_row_chunk<TO>(C + (int64_t)row * ldc + col, v, min(32, N - col), vec_c != 0, accumulate != 0);
+        for (int c = 0; c < BN2 / 32; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32b_x32(taddr + c * 32, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            __stcg(mine + (c * 8 + i) * BMC,
+                   make_float4(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]),
+                               __uint_as_float(v[4 * i + 2]), __uint_as_float(v[4 * i + 3])));
+        }
+        __threadfence();
+        epi_sync();
+        if (warp == 2 && lane == 0) *epi_word = atomicAdd(&tickets[it.tail * 2 + rank], 1u);
+        epi_sync();
+        write_c = epi_ok && (*epi_word == 1u);
+        if (write_c) __threadfence();
+        epi_sync();  // everybody has read the ticket before the next item overwrites it
+        if (write_c && warp == 2 && lane == 0) tickets[it.tail * 2 + rank] = 0;
+      }
+      if (write_c) {
+#pragma unroll 1
+        for (int c = 0; c < BN2 / 32; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32b_x32(taddr + c * 32, v);
+          tmem_ld_wait();
+          if (other != nullptr) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const float4 o = __ldcg(other + (c * 8 + i) * BMC);
+              v[4 * i] = __float_as_uint(__uint_as_float(v[4 * i]) + o.x);
+              v[4 * i + 1] = __float_as_uint(__uint_as_float(v[4 * i + 1]) + o.y);
+              v[4 * i + 2] = __float_as_uint(__uint_as_float(v[4 * i + 2]) + o.z);
+              v[4 * i + 3] = __float_as_uint(__uint_as_float(v[4 * i + 3]) + o.w);
+            }
+          }
+          const int col = n0 + c * 32;
+          if (row < M && col < N)
+            store_row_chunk<TO>(C + (int64_t)row * ldc + col, v, min(32, N - col), vec_c != 0, accumulate != 0);
+        }
       }
       tc_fence_before_sync();
       __syncwarp();
@@ -280,9 +351,36 @@ __global__ void __launch_bounds__(kThreads2, 1)
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+// Tail plan: `pairs` CTA pairs, `tiles` 256x256 tiles.  A partial last wave of at most pairs/2
+// tiles is run as twice as many K halves.
+struct TailPlan {
+  int pairs, n_full, n_items, tail_tiles;
+  size_t off_partials, bytes;
+};
+TailPlan make_tail_plan(const frisk_b200_gemm_desc& d, int pairs_available) {
+  GemmDims g = resolve_dims(d);
+  TailPlan t{};
+  int tiles = (int)(((g.M + BM2 - 1) / BM2) * ((g.N + BN2 - 1) / BN2));
+  t.pairs = tiles < pairs_available ? tiles : pairs_available;
+  t.n_full = t.n_items = tiles;
+  int rem = tiles % t.pairs;
+  int num_kb = (int)((g.K + BK - 1) / BK);
+  const char* e = getenv("FRISK_B200_GEMM_NO_TAIL_SPLIT");
+  if (tiles > t.pairs && rem > 0 && 2 * rem <= t.pairs && num_kb >= 8 && !(e && e[0] == '1')) {
+    t.tail_tiles = rem;
+    t.n_full = tiles - rem;
+    t.n_items = t.n_full + 2 * rem;
+  }
+  // tickets live in a fixed-size prefix so that a scratch buffer reused for another shape never
+  // finds old partial sums where it keeps tickets
+  t.off_partials = kTicketBytes;
+  t.bytes = t.tail_tiles ? t.off_partials + (size_t)t.tail_tiles * 2 * BM2 * BN2 * sizeof(float) : 0;
+  return t;
+}
+
 template <typename TO, bool BF16, bool A_MN, bool B_MN>
 int launch_cfg2(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc& d, const void* A, const void* B, void* C,
-                cudaStream_t s) {
+                void* ws, size_t ws_bytes, cudaStream_t s) {
   GemmDims g = resolve_dims(d);
   CUtensorMap ta, tb;
   int rc;
@@ -299,8 +397,6 @@ int launch_cfg2(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc& d, const void* 
 
   auto kern = gemm_tcgen05_2cta_kernel<TO, BF16, A_MN, B_MN>;
   FB_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem2::kTotal));
-  int tiles = (int)(((g.M + BM2 - 1) / BM2) * ((g.N + BN2 - 1) / BN2));
-
   cudaLaunchConfig_t cfg = {};
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -316,27 +412,37 @@ int launch_cfg2(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc& d, const void* 
   int max_clusters = 0;
   FB_CUDA(ctx, cudaOccupancyMaxActiveClusters(&max_clusters, kern, &cfg));
   if (max_clusters < 1) return FRISK_B200_E_UNSUPPORTED;
-  int pairs = tiles < max_clusters ? tiles : max_clusters;
-  cfg.gridDim = dim3(2 * pairs);
+  if (max_clusters > kPairsAssumed) max_clusters = kPairsAssumed;
+  TailPlan tp = make_tail_plan(d, max_clusters);
+  if (tp.bytes && (!ws || ws_bytes < tp.bytes)) {
+    // no scratch: run every tile whole
+    tp.n_full = tp.n_items = tp.n_full + tp.tail_tiles;
+    tp.tail_tiles = 0;
+  }
+  cfg.gridDim = dim3(2 * tp.pairs);
+  unsigned* tickets = static_cast<unsigned*>(ws);
+  float* partials = tp.tail_tiles ? reinterpret_cast<float*>(static_cast<unsigned char*>(ws) + tp.off_partials) : nullptr;
   int vec_c = aligned16(C) && (g.ldc * sizeof(TO)) % 16 == 0;
   TO* Cp = static_cast<TO*>(C);
   int Mi = (int)g.M, Ni = (int)g.N, Ki = (int)g.K, acc = d.clear_accum ? 0 : 1;
   int64_t ldc = g.ldc;
   unsigned* st = ctx->d_status;
-  FB_CUDA(ctx, cudaLaunchKernelEx(&cfg, kern, ta, tb, Cp, Mi, Ni, Ki, ldc, acc, vec_c, st));
+  int n_full = tp.n_full, n_items = tp.n_items;
+  FB_CUDA(ctx, cudaLaunchKernelEx(&cfg, kern, ta, tb, Cp, Mi, Ni, Ki, ldc, acc, vec_c, n_full, n_items, partials,
+                                  tickets, st));
   return 0;
 }
 
 template <typename TO, bool BF16>
 int launch_major2(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc& d, const void* A, const void* B, void* C,
-                  cudaStream_t s) {
+                  void* ws, size_t ws_bytes, cudaStream_t s) {
   bool a_mn = d.trans_a != 0, b_mn = d.trans_b == 0;
   if (a_mn) {
-    if (b_mn) return launch_cfg2<TO, BF16, true, true>(ctx, d, A, B, C, s);
-    return launch_cfg2<TO, BF16, true, false>(ctx, d, A, B, C, s);
+    if (b_mn) return launch_cfg2<TO, BF16, true, true>(ctx, d, A, B, C, ws, ws_bytes, s);
+    return launch_cfg2<TO, BF16, true, false>(ctx, d, A, B, C, ws, ws_bytes, s);
   }
-  if (b_mn) return launch_cfg2<TO, BF16, false, true>(ctx, d, A, B, C, s);
-  return launch_cfg2<TO, BF16, false, false>(ctx, d, A, B, C, s);
+  if (b_mn) return launch_cfg2<TO, BF16, false, true>(ctx, d, A, B, C, ws, ws_bytes, s);
+  return launch_cfg2<TO, BF16, false, false>(ctx, d, A, B, C, ws, ws_bytes, s);
 }
 
 }  // namespace
@@ -348,15 +454,24 @@ bool tcgen05_2cta_preferred(const frisk_b200_gemm_desc& d) {
   return tiles >= kNumSMsDefault / 2;
 }
 
+// Worst case over the number of CTA pairs the device grants (at most kPairsAssumed/2 tail tiles).
+size_t tcgen05_2cta_workspace_bytes(const frisk_b200_gemm_desc& d) {
+  GemmDims g = resolve_dims(d);
+  const int64_t tiles = ((g.M + BM2 - 1) / BM2) * ((g.N + BN2 - 1) / BN2);
+  if (tiles <= kPairsAssumed / 2 || (g.K + BK - 1) / BK < 8) return 0;
+  return kTicketBytes + (size_t)(kPairsAssumed / 2) * 2 * BM2 * BN2 * sizeof(float);
+}
+
 int launch_gemm_tcgen05_2cta(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc& d, const void* A, const void* B,
-                             void* C, cudaStream_t s) {
+                             void* C, void* ws, size_t ws_bytes, cudaStream_t s) {
   if (!tcgen05_supported(d)) return FRISK_B200_E_UNSUPPORTED;
   if (!aligned16(A) || !aligned16(B)) return FRISK_B200_E_ALIGN;
   const bool bf = d.dtype_ab == FRISK_B200_BF16;
   if (d.dtype_c == FRISK_B200_F32)
-    return bf ? launch_major2<float, true>(ctx, d, A, B, C, s) : launch_major2<float, false>(ctx, d, A, B, C, s);
-  if (bf) return launch_major2<__nv_bfloat16, true>(ctx, d, A, B, C, s);
-  return launch_major2<__half, false>(ctx, d, A, B, C, s);
+    return bf ? launch_major2<float, true>(ctx, d, A, B, C, ws, ws_bytes, s)
+              : launch_major2<float, false>(ctx, d, A, B, C, ws, ws_bytes, s);
+  if (bf) return launch_major2<__nv_bfloat16, true>(ctx, d, A, B, C, ws, ws_bytes, s);
+  return launch_major2<__half, false>(ctx, d, A, B, C, ws, ws_bytes, s);
 }
 
 }  // namespace fb

@@ -124,6 +124,21 @@ def test_tc_tail_wave_of_half_tiles(ctx, tb):
     check(ctx, 2048, 2400, 64, "fp16", "fp32", False, tb, 30, algo=capi.ALGO_TCGEN05, dist="normal_rsqrt_k")
 
 
+@pytest.mark.parametrize("tb", [True, False])
+def test_tc_pair_tail_wave_split_in_k(ctx, tb):
+    # 8 x 10 = 80 tiles of 256x256 on 74 CTA pairs: the 6 tiles of the last wave run as 12 K halves
+    # that meet through the fp32 scratch
+    P = capi.ALGO_TCGEN05_PAIR
+    check(ctx, 2048, 2560, 512, "bf16", "bf16", False, tb, 36, algo=P, dist="normal_rsqrt_k")
+    check(ctx, 2048, 2560, 1024, "fp16", "fp32", False, tb, 37, accumulate=True, algo=P, dist="normal_rsqrt_k")
+    check(ctx, 2000, 2500 // 8 * 8, 576, "fp16", "fp16", False, tb, 38, algo=P, dist="normal_rsqrt_k")
+    a, b = inputs.gemm_inputs(2048, 2560, 512, "bf16", False, tb, 39, "normal_rsqrt_k")
+    first, _ = run_gemm(ctx, a, b, "bf16", "bf16", 2048, 2560, 512, False, tb, algo=P)
+    for _ in range(3):  # tickets must be clean again after every launch; the sum is order-independent
+        again, ok = run_gemm(ctx, a, b, "bf16", "bf16", 2048, 2560, 512, False, tb, algo=P)
+        assert ok and np.array_equal(first, again)
+
+
 def test_tc_config_4096_nt(ctx):
     """Full benchmark size: rows sampled against the fp64 oracle, the whole matrix against
     size-independent properties (deterministic rerun; C(2A) = 2C exactly in fp16)."""
@@ -189,6 +204,20 @@ def test_gemm_host_entry(ctx):
     desc = capi.gemm_desc(256, 512, 128, "fp16", "fp16", False, True)
     ctx.gemm_host(desc, a.ctypes.data, b.ctypes.data, c.ctypes.data)
     assert rel_frobenius(c, gemm_oracle.gemm_fp64(a, b, "fp16", False, True)) <= TOL["fp16"]
+
+
+def test_gemm_host_entry_pipelined_panels(ctx):
+    # large enough that the host entry moves A and C in row panels that overlap the kernels
+    rng = np.random.default_rng(43)
+    for (M, N, K, dt, acc) in ((4096, 1024, 512, "fp16", False), (3000, 1024, 520, "bf16", True),
+                               (2048, 1024, 1024, "fp32", False)):
+        a, b = inputs.gemm_inputs(M, N, K, dt, False, True, 44, "normal_rsqrt_k" if dt != "fp32" else "uniform")
+        c0 = to_storage(rng.standard_normal((M, N), dtype=np.float32), dt) if acc else None
+        c = c0.copy() if acc else np.zeros((M, N), a.dtype)
+        desc = capi.gemm_desc(M, N, K, dt, dt, False, True, clear_accum=not acc)
+        ctx.gemm_host(desc, a.ctypes.data, b.ctypes.data, c.ctypes.data)
+        ref = gemm_oracle.gemm_fp64(a, b, dt, False, True, c0, dt)
+        assert rel_frobenius(from_storage(c, dt), ref) <= TOL[dt], (M, N, K, dt)
 
 
 def test_contract_errors_before_launch(ctx):
