@@ -40,7 +40,7 @@ class GemmDesc(ctypes.Structure):
 class AttnDesc(ctypes.Structure):
     _fields_ = [("B", ctypes.c_int32), ("H", ctypes.c_int32), ("S_q", ctypes.c_int32), ("S_kv", ctypes.c_int32),
                 ("D", ctypes.c_int32), ("scale", ctypes.c_float), ("causal", ctypes.c_int32),
-                ("dtype_in", ctypes.c_int32), ("dtype_out", ctypes.c_int32)]
+                ("dtype_in", ctypes.c_int32), ("dtype_out", ctypes.c_int32), ("normalize_p", ctypes.c_int32)]
 
 
 _lib = None
@@ -114,10 +114,10 @@ def gemm_desc(M, N, K, dtype_ab, dtype_c=None, trans_a=False, trans_b=False, cle
     return GemmDesc(M, N, K, int(trans_a), int(trans_b), int(clear_accum), code_ab, code_c, lda, ldb, ldc, 0, algo)
 
 
-def attn_desc(B, H, S_q, S_kv, D, scale, causal, dtype_in, dtype_out=None):
+def attn_desc(B, H, S_q, S_kv, D, scale, causal, dtype_in, dtype_out=None, normalize_p=False):
     code_in = DTYPE_CODE[dtype_in] if isinstance(dtype_in, str) else dtype_in
     code_out = code_in if dtype_out is None else (DTYPE_CODE[dtype_out] if isinstance(dtype_out, str) else dtype_out)
-    return AttnDesc(B, H, S_q, S_kv, D, float(scale), int(bool(causal)), code_in, code_out)
+    return AttnDesc(B, H, S_q, S_kv, D, float(scale), int(bool(causal)), code_in, code_out, int(bool(normalize_p)))
 
 
 class Context:

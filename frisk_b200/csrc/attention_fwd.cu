@@ -57,8 +57,9 @@ struct AttnSmem {
 
 struct AttnParams {
   int S_q, S_kv, n_pairs, causal;
+  int normalized;  // 1: two passes over the keys, P divided by the complete row sum before it is rounded
   int64_t total_ctas;
-  float scale_log2;
+  float scale_log2, scale;
   void* O;
   unsigned* status;
 };
@@ -139,7 +140,7 @@ __device__ __forceinline__ int kv_tiles_for(int m0, int S_q, int S_kv, int causa
   return min(all, last_key / BN + 1);
 }
 
-template <bool BF16, int D, bool OUT_F32>
+template <bool BF16, int D, bool OUT_F32, bool NORM>
 __global__ void __launch_bounds__(kThreads, 1)
     attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                          const __grid_constant__ CUtensorMap tmap_v, const AttnParams p) {
@@ -168,6 +169,9 @@ __global__ void __launch_bounds__(kThreads, 1)
   const int m0 = pair * 2 * BM;
   const int nq[2] = {kv_tiles_for(m0, p.S_q, p.S_kv, p.causal), kv_tiles_for(m0 + BM, p.S_q, p.S_kv, p.causal)};
   const int n_max = max(nq[0], nq[1]);
+  // Normalised mode runs the key loop twice: pass 0 only gathers row maxima and row sums, pass 1
+  // is the pass every mode has.  Barrier phases keep counting across the passes.
+  constexpr int first_pass = NORM ? 0 : 1;
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
@@ -208,24 +212,31 @@ __global__ void __launch_bounds__(kThreads, 1)
 #pragma unroll
         for (int b = 0; b < kBoxes; ++b)
           tma_load_3d(smem + L::kQ + q * L::kTileBytes + b * kBoxBytes, &tmap_q, q_full, b * 64, m0 + q * BM, bh);
-      int stage = 0;
-      uint32_t phase = 0;
-      for (int j = 0; j < n_max; ++j) {
-        if (!mbar_wait(&k_empty[stage], phase ^ 1, abort_flag, p.status, ST_ATTN_KV)) break;
-        mbar_expect_tx(&k_full[stage], L::kTileBytes);
+      int kt = 0, vt = 0;  // K / V tiles loaded so far (K is streamed once per pass)
+      bool ok = true;
+      for (int pass = first_pass; pass < 2 && ok; ++pass) {
+        for (int j = 0; j < n_max; ++j) {
+          const int ks = kt % kStagesKV;
+          if (!mbar_wait(&k_empty[ks], ((kt / kStagesKV) & 1) ^ 1, abort_flag, p.status, ST_ATTN_KV)) {
+            ok = false;
+            break;
+          }
+          mbar_expect_tx(&k_full[ks], L::kTileBytes);
 #pragma unroll
-        for (int b = 0; b < kBoxes; ++b)
-          tma_load_3d(smem + L::kK + stage * L::kTileBytes + b * kBoxBytes, &tmap_k, &k_full[stage], b * 64,
-                      j * BN, bh);
-        if (!mbar_wait(&v_empty[stage], phase ^ 1, abort_flag, p.status, ST_ATTN_KV)) break;
-        mbar_expect_tx(&v_full[stage], L::kTileBytes);
+          for (int b = 0; b < kBoxes; ++b)
+            tma_load_3d(smem + L::kK + ks * L::kTileBytes + b * kBoxBytes, &tmap_k, &k_full[ks], b * 64, j * BN, bh);
+          ++kt;
+          if (pass == 0) continue;  // the statistics pass needs no values
+          const int vs = vt % kStagesKV;
+          if (!mbar_wait(&v_empty[vs], ((vt / kStagesKV) & 1) ^ 1, abort_flag, p.status, ST_ATTN_KV)) {
+            ok = false;
+            break;
+          }
+          mbar_expect_tx(&v_full[vs], L::kTileBytes);
 #pragma unroll
-        for (int b = 0; b < kBoxes; ++b)
-          tma_load_3d(smem + L::kV + stage * L::kTileBytes + b * kBoxBytes, &tmap_v, &v_full[stage], b * 64,
-                      j * BN, bh);
-        if (++stage == kStagesKV) {
-          stage = 0;
-          phase ^= 1;
+          for (int b = 0; b < kBoxes; ++b)
+            tma_load_3d(smem + L::kV + vs * L::kTileBytes + b * kBoxBytes, &tmap_v, &v_full[vs], b * 64, j * BN, bh);
+          ++vt;
         }
       }
     }
@@ -267,13 +278,18 @@ __global__ void __launch_bounds__(kThreads, 1)
 
       // O_q += P_q(j) . V(j).  The softmax group publishes P in two halves (64 keys each), so
       // the first four k16 slices start while the second half is still being exponentiated.
+      int pass_index = 0;       // 0 for the first pass that runs, 1 for the second
+      bool stats_pass = false;  // the pass that only gathers statistics issues no P.V
       auto issue_pv = [&](int q, int stage, int j) {
         const uint32_t d_tmem = tmem_base + 256 + q * 128;
         const uint32_t a_tmem = tmem_base + q * 128;  // P_q: 8 columns per k16 slice
         const uint64_t dv = stage ? dv1 : dv0;
+        const uint32_t parity = (pass_index * nq[q] + j) & 1;
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
-          if (ok) ok = mbar_wait(half ? &p_ready_hi[q] : &p_ready[q], j & 1, abort_flag, p.status, ST_ATTN_P);
+          // in the statistics pass this only learns that the softmax group is done with S_q
+          if (ok) ok = mbar_wait(half ? &p_ready_hi[q] : &p_ready[q], parity, abort_flag, p.status, ST_ATTN_P);
+          if (stats_pass) continue;
           if (half == 0) ensure_v(j);
           if (!ok) return;
           tc_fence_after_sync();
@@ -282,31 +298,35 @@ __global__ void __launch_bounds__(kThreads, 1)
             umma_f16_ts(d_tmem, a_tmem + kk * 8, dv + static_cast<uint64_t>((kk * 2048) >> 4), idesc_o,
                         (j | kk) != 0);
         }
-        umma_commit(&o_done[q]);
+        if (!stats_pass) umma_commit(&o_done[q]);
       };
 
-      for (int j = 0; j < n_max && ok; ++j) {
-        const int stage = j % kStagesKV;
-        ok = mbar_wait(&k_full[stage], (j / kStagesKV) & 1, abort_flag, p.status, ST_ATTN_KV);
-        if (!ok) break;
-        tc_fence_after_sync();
-        if (j < nq[0]) issue_s(0, stage);
-        if (j >= 1 && j - 1 < nq[1]) {  // O1 += P1(j-1) . V(j-1)
-          issue_pv(1, (j - 1) % kStagesKV, j - 1);
+      for (int pass = first_pass; pass < 2 && ok; ++pass, ++pass_index) {
+        stats_pass = pass == 0;
+        const int kbase = pass_index * n_max;  // K tiles consumed by the earlier pass
+        for (int j = 0; j < n_max && ok; ++j) {
+          const int stage = (kbase + j) % kStagesKV;  // K stage; V tiles only exist in the last pass: stage j % 2
+          ok = mbar_wait(&k_full[stage], ((kbase + j) / kStagesKV) & 1, abort_flag, p.status, ST_ATTN_KV);
           if (!ok) break;
+          tc_fence_after_sync();
+          if (j < nq[0]) issue_s(0, stage);
+          if (j >= 1 && j - 1 < nq[1]) {  // O1 += P1(j-1) . V(j-1)
+            issue_pv(1, (j - 1) % kStagesKV, j - 1);
+            if (!ok) break;
+          }
+          if (j >= 1 && !stats_pass) umma_commit(&v_empty[(j - 1) % kStagesKV]);  // both P.V of tile j-1 are issued
+          if (j < nq[1]) issue_s(1, stage);
+          umma_commit(&k_empty[stage]);  // both S of tile j are issued
+          if (j < nq[0]) {               // O0 += P0(j) . V(j)
+            issue_pv(0, j % kStagesKV, j);
+            if (!ok) break;
+          }
         }
-        if (j >= 1) umma_commit(&v_empty[(j - 1) % kStagesKV]);  // both P.V of tile j-1 are issued
-        if (j < nq[1]) issue_s(1, stage);
-        umma_commit(&k_empty[stage]);  // both S of tile j are issued
-        if (j < nq[0]) {               // O0 += P0(j) . V(j)
-          issue_pv(0, stage, j);
-          if (!ok) break;
+        if (ok && n_max >= 1) {
+          const int j = n_max - 1;
+          if (j < nq[1]) issue_pv(1, j % kStagesKV, j);
+          if (ok && !stats_pass) umma_commit(&v_empty[j % kStagesKV]);
         }
-      }
-      if (ok && n_max >= 1) {
-        const int j = n_max - 1;
-        if (j < nq[1]) issue_pv(1, j % kStagesKV, j);
-        umma_commit(&v_empty[j % kStagesKV]);
       }
     }
   }
@@ -328,6 +348,82 @@ __global__ void __launch_bounds__(kThreads, 1)
     float l_sum = 0.f;
     bool ok = true;
 
+    if (NORM) {
+      // The reference's semantics (benchmark/layout/execution/tiled_attention.py:697-698,
+      // tail_attention_reference.py:74-78): score = fp32(dot) * scale; subtract the maximum of the
+      // WHOLE row; e = ex2((score - max) * log2e); p = e / (sum of e over the whole row), IEEE
+      // division; p rounded to 16 bits; then P.V.  Pass 0 finds max and sum, pass 1 forms P.
+      const float kLog2e = 1.44269504088896340736f;
+      float m_run = -INFINITY, l_run = 0.f;
+      for (int pass = 0; pass < 2 && ok; ++pass) {
+        for (int j = 0; j < n_tiles; ++j) {
+          if (!mbar_wait(&s_full[q], (pass * n_tiles + j) & 1, abort_flag, p.status, ST_ATTN_S)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          uint32_t sr[4][32];
+#pragma unroll
+          for (int c = 0; c < 4; ++c) tmem_ld_32x32b_x32(t_s + c * 32, sr[c]);
+          tmem_ld_wait();
+          const int n0 = j * BN;
+          int limit = p.S_kv - 1;
+          if (p.causal) limit = min(limit, g_row + off);
+          limit -= n0;
+          if (pass == 0) {
+            // S_q is in registers: the MMA warp may overwrite it
+            tc_fence_before_sync();
+            mbar_arrive(&p_ready[q]);
+            mbar_arrive(&p_ready_hi[q]);
+            float mx = -INFINITY;
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+#pragma unroll
+              for (int i = 0; i < 32; ++i) {
+                float sc = (c * 32 + i > limit) ? -INFINITY : __fmul_rn(__uint_as_float(sr[c][i]), p.scale);
+                sr[c][i] = __float_as_uint(sc);
+                mx = fmaxf(mx, sc);
+              }
+            const float m_new = fmaxf(m_run, mx);
+            float sum = 0.f;
+            if (m_new != -INFINITY) {
+#pragma unroll
+              for (int c = 0; c < 4; ++c)
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                  sum += ex2f(__fmul_rn(__fsub_rn(__uint_as_float(sr[c][i]), m_new), kLog2e));
+              const float carry = (m_run == -INFINITY) ? 0.f : l_run * ex2f(__fmul_rn(__fsub_rn(m_run, m_new), kLog2e));
+              l_run = carry + sum;
+              m_run = m_new;
+            }
+          } else {
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              uint32_t pk[16];
+#pragma unroll
+              for (int i = 0; i < 16; ++i) {
+                float pv[2];
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                  const int col = c * 32 + 2 * i + e;
+                  const float sc = __fmul_rn(__uint_as_float(sr[c][2 * i + e]), p.scale);
+                  const float ex = (col > limit) ? 0.f : ex2f(__fmul_rn(__fsub_rn(sc, m_run), kLog2e));
+                  pv[e] = __fdiv_rn(ex, l_run);
+                }
+                pk[i] = pack16<BF16>(pv[0], pv[1]);
+              }
+              tmem_st_32x32b_x16(t_s + c * 16, pk);
+              if (c & 1) {
+                tmem_st_wait();
+                tc_fence_before_sync();
+                mbar_arrive(c == 1 ? &p_ready[q] : &p_ready_hi[q]);
+              }
+            }
+          }
+        }
+      }
+      l_sum = 1.0f;  // P is already normalised
+    } else
     for (int j = 0; j < n_tiles; ++j) {
       if (!mbar_wait(&s_full[q], j & 1, abort_flag, p.status, ST_ATTN_S)) {
         ok = false;
@@ -467,7 +563,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   }
 }
 
-template <bool BF16, int D, bool OUT_F32>
+template <bool BF16, int D, bool OUT_F32, bool NORM>
 int launch_cfg(frisk_b200_ctx* ctx, const frisk_b200_attn_desc& d, const void* Q, const void* K, const void* V,
                void* O, cudaStream_t s) {
   CUtensorMap tq, tk, tv;
@@ -487,10 +583,12 @@ int launch_cfg(frisk_b200_ctx* ctx, const frisk_b200_attn_desc& d, const void* Q
   p.causal = d.causal ? 1 : 0;
   p.total_ctas = (int64_t)p.n_pairs * bh;
   p.scale_log2 = d.scale * 1.4426950408889634f;
+  p.scale = d.scale;
+  p.normalized = d.normalize_p ? 1 : 0;
   p.O = O;
   p.status = ctx->d_status;
   if (p.total_ctas > INT32_MAX) return FRISK_B200_E_ATTN_SHAPE;
-  auto kern = attention_fwd_kernel<BF16, D, OUT_F32>;
+  auto kern = attention_fwd_kernel<BF16, D, OUT_F32, NORM>;
   using L = AttnSmem<D>;
   // setmaxnreg.inc waits (without a bound) until the CTA's own register pool holds what it
   // asks for: the registers the TMA/MMA warpgroup (128 threads) gives up must cover what the
@@ -510,8 +608,12 @@ int launch_cfg(frisk_b200_ctx* ctx, const frisk_b200_attn_desc& d, const void* Q
 template <bool BF16, int D>
 int launch_out(frisk_b200_ctx* ctx, const frisk_b200_attn_desc& d, const void* Q, const void* K, const void* V,
                void* O, cudaStream_t s) {
-  if (d.dtype_out == FRISK_B200_F32) return launch_cfg<BF16, D, true>(ctx, d, Q, K, V, O, s);
-  return launch_cfg<BF16, D, false>(ctx, d, Q, K, V, O, s);
+  if (d.normalize_p) {
+    if (d.dtype_out == FRISK_B200_F32) return launch_cfg<BF16, D, true, true>(ctx, d, Q, K, V, O, s);
+    return launch_cfg<BF16, D, false, true>(ctx, d, Q, K, V, O, s);
+  }
+  if (d.dtype_out == FRISK_B200_F32) return launch_cfg<BF16, D, true, false>(ctx, d, Q, K, V, O, s);
+  return launch_cfg<BF16, D, false, false>(ctx, d, Q, K, V, O, s);
 }
 
 }  // namespace

@@ -171,8 +171,10 @@ def attention_geometry(spec):
     return spec["B"], spec["H"], spec["N"], spec["D"]
 
 
-def attention_forward(spec, q, k, v, out, *, scale=None, causal=False, stream=None):
-    """O = softmax(scale * Q K^T [+causal]) V on compact BHSD CUDA tensors."""
+def attention_forward(spec, q, k, v, out, *, scale=None, causal=False, normalize_p=False, stream=None):
+    """O = softmax(scale * Q K^T [+causal]) V on compact BHSD CUDA tensors.
+    ``normalize_p`` selects the reference's two-pass semantics (P divided by the whole row sum
+    before it is rounded to 16 bits, ``tiled_attention.py:697-698``) instead of the single pass."""
     torch = _torch()
     b, h, n, d = attention_geometry(spec)
     n_kv = int(spec.get("N_kv", n))
@@ -184,7 +186,7 @@ def attention_forward(spec, q, k, v, out, *, scale=None, causal=False, stream=No
         raise ValueError("attention inputs must share one 16-bit float type")
     if scale is None:
         scale = 1.0 / math.sqrt(d)
-    desc = capi.attn_desc(b, h, n, n_kv, d, scale, causal, code[q.dtype], code[out.dtype])
+    desc = capi.attn_desc(b, h, n, n_kv, d, scale, causal, code[q.dtype], code[out.dtype], normalize_p)
     ctx = context_for(out.device.index or 0)
     ctx.attention_fwd(desc, q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
                       stream=_stream_ptr(stream, out.device))

@@ -94,6 +94,12 @@ typedef struct frisk_b200_attn_desc {
   int32_t causal;
   int32_t dtype_in;  /* F16 or BF16                      */
   int32_t dtype_out; /* == dtype_in, or F32              */
+  /* 0: single pass, P rounded relative to a running maximum (fast path).
+   * 1: the reference's semantics to the letter: two passes over the keys, every probability is
+   *    divided by the COMPLETE row sum (IEEE division) before it is rounded to 16 bits
+   *    (tiled_attention.py:697-698, tail_attention_reference.py:74-78); the reference's analytic
+   *    fixtures then match bit for bit. */
+  int32_t normalize_p;
 } frisk_b200_attn_desc;
 
 /* ---- context -------------------------------------------------------------------------

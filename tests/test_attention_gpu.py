@@ -118,6 +118,49 @@ def test_reference_fixtures_d64(ctx):
             assert (err <= 2e-3 + 2e-3 * np.abs(ref)).all(), key  # the single-tile checker's bound
 
 
+def test_reference_fixtures_normalized_mode(ctx):
+    """normalize_p = 1 reproduces the reference's own semantics (P divided by the complete row sum
+    before it is rounded): its analytic fixtures come out bit for bit, and every fixture is inside
+    the bounds of the reference's own checker (tail_attention_reference.check_output)."""
+    import torch
+    g = np.load(GOLDEN / "attention_tiled_d64.npz")
+    s = torch.cuda.current_stream().cuda_stream
+    for name in ("random", "uniform-sparse-value", "last-key-dominant", "tail-uniform", "key-boundary",
+                 "neutral-extension"):
+        for n in (64, 65, 130):
+            key = f"{name}/n{n}"
+            q, k, v = g[key + "/q"], g[key + "/k"], g[key + "/v"]
+            gq, gk, gv = (Guarded(x.shape, "fp16", fill=x) for x in (q, k, v))
+            go = Guarded(q.shape, "fp32")
+            go.view.fill_(float("nan"))
+            desc = capi.attn_desc(q.shape[0], q.shape[1], n, n, 64, 0.125, False, "fp16", "fp32", normalize_p=True)
+            ctx.attention_fwd(desc, gq.view.data_ptr(), gk.view.data_ptr(), gv.view.data_ptr(), go.view.data_ptr(),
+                              stream=s)
+            ctx.check(s)
+            got = go.host()
+            assert go.guards_intact() and np.isfinite(got).all(), key
+            assert ao.within_reference_tolerance(got, g[key + "/strict"], "strict") <= 1.0, key
+            assert ao.within_reference_tolerance(got, g[key + "/fp64"], "fp64") <= 1.0, key
+            if name in ("uniform-sparse-value", "last-key-dominant", "tail-uniform"):
+                assert np.array_equal(got.view(np.uint32), g[key + "/strict"].view(np.uint32)), key
+
+
+def test_normalized_mode_large_heads(ctx):
+    # the two-pass mode on the benchmark's head shape (bf16, D=128, causal) against the strict oracle
+    rng = np.random.default_rng(12)
+    from oracle.numerics import to_storage
+    import torch
+    q, k, v = (to_storage(rng.standard_normal((1, 2, 700, 128), dtype=np.float32), "bf16") for _ in range(3))
+    gq, gk, gv = (Guarded(x.shape, "bf16", fill=x) for x in (q, k, v))
+    go = Guarded(q.shape, "fp32")
+    desc = capi.attn_desc(1, 2, 700, 700, 128, 128 ** -0.5, True, "bf16", "fp32", normalize_p=True)
+    s = torch.cuda.current_stream().cuda_stream
+    ctx.attention_fwd(desc, gq.view.data_ptr(), gk.view.data_ptr(), gv.view.data_ptr(), go.view.data_ptr(), stream=s)
+    ctx.check(s)
+    ref = ao.attention_fwd(q, k, v, "bf16", 128 ** -0.5, causal=True, mode="strict")
+    assert rel_frobenius(go.host(), ref) <= 2e-3
+
+
 def test_properties_small(ctx):
     rng = np.random.default_rng(11)
     from oracle.numerics import to_storage
