@@ -289,24 +289,43 @@ def run_ours(args):
 
 
 def splitk_secondary(ctx, torch, dist, world, rank, peaks):
-    """bf16 GEMM M=N=8192, K=131072 with K split across the ranks: fp32 partials from the
-    tcgen05 kernel, NCCL reduce-scatter pipelined over row panels, local rounding to bf16."""
+    """bf16 GEMM M=N=8192, K=131072 with K split across the ranks, two ways: (fused) the tcgen05
+    epilogue adds each fp32 tile into the row owner's memory over NVLink; (nccl) fp32 partials,
+    NCCL reduce-scatter pipelined over row panels, local rounding to bf16."""
     from frisk_b200 import splitk
-    try:
-        M, N, K = 8192, 8192, 131072
-        plan = splitk.make_plan(M, N, K, world, rank, panels=4)
-        a = torch.randn(M, plan.k_local, device="cuda", dtype=torch.bfloat16) * (1 / math.sqrt(K))
-        b = torch.randn(N, plan.k_local, device="cuda", dtype=torch.bfloat16)
-        op = splitk.SplitKGemm(plan, "bf16", ctx=ctx, group=dist.group.WORLD)
-        total, per, _ = time_steps(lambda i: op.run(a, b), 5, 3, torch, dist, world)
-        ms = total / 5
+    M, N, K = 8192, 8192, 131072
+    res = {"n_gpus": world}
+
+    def line(ms, exchange):
         tf = 2.0 * M * N * K / ms / 1e9
-        return {"ms": round(ms, 4), "tflops": round(tf, 2), "n_gpus": world, "panels": plan.panels,
+        return {"ms": round(ms, 4), "tflops": round(tf, 2),
                 "per_gpu_frac_of_measured_sustained": round(tf / world / peaks["bf16_tflops_sustained"], 4),
-                "exchange": "NCCL reduce_scatter of fp32 partials, %.1f MB sent per GPU" %
-                            ((world - 1) / world * M * N * 4 / 1e6)}
+                "exchange": exchange}
+    sent = (world - 1) / world * M * N * 4 / 1e6
+    try:
+        k_local = K // world
+        a = torch.randn(M, k_local, device="cuda", dtype=torch.bfloat16) * (1 / math.sqrt(K))
+        b = torch.randn(N, k_local, device="cuda", dtype=torch.bfloat16)
     except Exception as e:  # noqa: BLE001
         return {"error": str(e)}
+    try:
+        op = splitk.SplitKGemmPush(M, N, K, world, rank, "bf16", ctx, dist.group.WORLD)
+        total, per, _ = time_steps(lambda i: op.run(a, b), 5, 3, torch, dist, world)
+        ctx.check(torch.cuda.current_stream().cuda_stream)
+        res["fused_push"] = line(total / 5, "epilogue red.global.add.v4.f32 into peer memory, %.1f MB sent per GPU" % sent)
+        dist.barrier()
+        op.close()
+    except Exception as e:  # noqa: BLE001
+        res["fused_push"] = {"error": str(e)}
+    try:
+        plan = splitk.make_plan(M, N, K, world, rank, panels=4)
+        op = splitk.SplitKGemm(plan, "bf16", ctx=ctx, group=dist.group.WORLD)
+        total, per, _ = time_steps(lambda i: op.run(a, b), 5, 3, torch, dist, world)
+        res["nccl"] = line(total / 5, "NCCL reduce_scatter of fp32 partials over %d row panels, %.1f MB sent per GPU"
+                           % (plan.panels, sent))
+    except Exception as e:  # noqa: BLE001
+        res["nccl"] = {"error": str(e)}
+    return res
 
 
 def secondary(ctx, torch, stream, peaks, args):

@@ -25,7 +25,8 @@ EXPORTS = (
     "frisk_b200_gemm_select", "frisk_b200_gemm_workspace_bytes", "frisk_b200_gemm", "frisk_b200_gemm_host",
     "frisk_b200_attention_validate", "frisk_b200_attention_workspace_bytes", "frisk_b200_attention_fwd",
     "frisk_b200_attention_fwd_host", "frisk_b200_convert_f32", "frisk_b200_check",
-    "frisk_b200_gemm_skinny_static",
+    "frisk_b200_gemm_skinny_static", "frisk_b200_gemm_push", "frisk_b200_convert_f32_clear",
+    "frisk_b200_peer_buffer_create", "frisk_b200_peer_buffer_open", "frisk_b200_peer_buffer_close",
 )
 
 
@@ -81,6 +82,11 @@ def load():
         "frisk_b200_convert_f32": (ctypes.c_int, [vp, vp, vp, i64, i32, vp]),
         "frisk_b200_check": (ctypes.c_int, [vp, vp]),
         "frisk_b200_gemm_skinny_static": (ctypes.c_int, [ctypes.c_int, gd, vp, vp, vp, vp]),
+        "frisk_b200_gemm_push": (ctypes.c_int, [vp, gd, vp, vp, ctypes.POINTER(vp), i32, i64, i64, vp]),
+        "frisk_b200_convert_f32_clear": (ctypes.c_int, [vp, vp, vp, i64, i32, vp]),
+        "frisk_b200_peer_buffer_create": (ctypes.c_int, [vp, sz, ctypes.POINTER(vp), vp]),
+        "frisk_b200_peer_buffer_open": (ctypes.c_int, [vp, vp, ctypes.POINTER(vp)]),
+        "frisk_b200_peer_buffer_close": (ctypes.c_int, [vp, vp, i32]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(lib, name)
@@ -165,6 +171,32 @@ class Context:
     def convert_f32(self, src_ptr, dst_ptr, count, dtype, stream=None):
         code = DTYPE_CODE[dtype] if isinstance(dtype, str) else dtype
         raise_for(load().frisk_b200_convert_f32(self.handle, src_ptr, dst_ptr, count, code, stream), self._h)
+
+    def gemm_push(self, desc, a_ptr, b_ptr, targets, rows_per_target, ld_target, stream=None):
+        arr = (ctypes.c_void_p * len(targets))(*targets)
+        rc = load().frisk_b200_gemm_push(self.handle, ctypes.byref(desc), a_ptr, b_ptr, arr, len(targets),
+                                         rows_per_target, ld_target, stream)
+        raise_for(rc, self._h)
+
+    def convert_f32_clear(self, src_ptr, dst_ptr, count, dtype, stream=None):
+        code = DTYPE_CODE[dtype] if isinstance(dtype, str) else dtype
+        raise_for(load().frisk_b200_convert_f32_clear(self.handle, src_ptr, dst_ptr, count, code, stream), self._h)
+
+    def peer_buffer_create(self, nbytes):
+        """-> (device pointer, 64-byte handle) of a zeroed buffer other processes can map."""
+        ptr = ctypes.c_void_p()
+        handle = ctypes.create_string_buffer(64)
+        raise_for(load().frisk_b200_peer_buffer_create(self.handle, nbytes, ctypes.byref(ptr), handle), self._h)
+        return ptr.value, handle.raw
+
+    def peer_buffer_open(self, handle):
+        ptr = ctypes.c_void_p()
+        buf = ctypes.create_string_buffer(handle, 64)
+        raise_for(load().frisk_b200_peer_buffer_open(self.handle, buf, ctypes.byref(ptr)), self._h)
+        return ptr.value
+
+    def peer_buffer_close(self, ptr, owned):
+        raise_for(load().frisk_b200_peer_buffer_close(self.handle, ptr, int(bool(owned))), self._h)
 
     def check(self, stream=None):
         raise_for(load().frisk_b200_check(self.handle, stream), self._h)

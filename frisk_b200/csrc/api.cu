@@ -86,6 +86,45 @@ __global__ void convert_f32_kernel(const float* __restrict__ src, T* __restrict_
 }
 }  // namespace
 
+namespace {
+// round and clear in one pass: the accumulation buffer is ready for the next product
+template <typename T>
+__global__ void convert_f32_clear_kernel(float* __restrict__ src, T* __restrict__ dst, int64_t n) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  const int64_t n8 = n / 8;
+  const bool vec = (reinterpret_cast<uintptr_t>(src) & 15u) == 0 && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0;
+  if (vec) {
+    for (int64_t v = i; v < n8; v += stride) {
+      float4 a = reinterpret_cast<const float4*>(src)[2 * v];
+      float4 b = reinterpret_cast<const float4*>(src)[2 * v + 1];
+      T o[8] = {T(a.x), T(a.y), T(a.z), T(a.w), T(b.x), T(b.y), T(b.z), T(b.w)};
+      reinterpret_cast<uint4*>(dst)[v] = *reinterpret_cast<uint4*>(o);
+      reinterpret_cast<float4*>(src)[2 * v] = make_float4(0.f, 0.f, 0.f, 0.f);
+      reinterpret_cast<float4*>(src)[2 * v + 1] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+  }
+  for (int64_t k = (vec ? n8 * 8 : 0) + i; k < n; k += stride) {
+    dst[k] = T(src[k]);
+    src[k] = 0.f;
+  }
+}
+}  // namespace
+
+int launch_convert_f32_clear(float* src, void* dst, int64_t n, int dtype, cudaStream_t s) {
+  if (n <= 0) return 0;
+  int blocks = (int)((n / 8 + 255) / 256);
+  if (blocks < 1) blocks = 1;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (dtype == FRISK_B200_F16)
+    convert_f32_clear_kernel<__half><<<blocks, 256, 0, s>>>(src, static_cast<__half*>(dst), n);
+  else if (dtype == FRISK_B200_BF16)
+    convert_f32_clear_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>(src, static_cast<__nv_bfloat16*>(dst), n);
+  else
+    return FRISK_B200_E_UNSUPPORTED;
+  return cudaGetLastError() == cudaSuccess ? 0 : FRISK_B200_E_CUDA;
+}
+
 int launch_convert_f32(const float* src, void* dst, int64_t n, int dtype, cudaStream_t s) {
   if (n <= 0) return 0;
   int blocks = (int)((n / 8 + 255) / 256);
@@ -522,6 +561,69 @@ int frisk_b200_attention_fwd_host(frisk_b200_ctx* ctx, const frisk_b200_attn_des
     cudaStreamSynchronize(s);
     return FRISK_B200_E_DEVICE_TIMEOUT;
   }
+  return 0;
+}
+
+int frisk_b200_gemm_push(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc* d, const void* A, const void* B,
+                         float* const* targets, int32_t n_targets, int64_t rows_per_target, int64_t ld_target,
+                         void* stream) {
+  if (!ctx || !d || !A || !B || !targets) return FRISK_B200_E_ARG;
+  int rc = frisk_b200_gemm_validate(d);
+  if (rc) return rc;
+  if (n_targets < 1 || n_targets > 8 || rows_per_target < 1 || rows_per_target * n_targets < d->M ||
+      rows_per_target > INT32_MAX || ld_target < d->N)
+    return FRISK_B200_E_ARG;
+  PushTargets push{};
+  for (int i = 0; i < n_targets; ++i) {
+    if (!targets[i]) return FRISK_B200_E_ARG;
+    if (reinterpret_cast<uintptr_t>(targets[i]) & 15u) return FRISK_B200_E_ALIGN;
+    push.ptr[i] = targets[i];
+  }
+  push.n = n_targets;
+  push.rows_per_target = (int)rows_per_target;
+  push.ld = ld_target;
+  FB_CUDA(ctx, cudaSetDevice(ctx->device));
+  return launch_gemm_tcgen05_2cta_push(ctx, *d, A, B, push, static_cast<cudaStream_t>(stream));
+}
+
+int frisk_b200_convert_f32_clear(frisk_b200_ctx* ctx, float* src, void* dst, int64_t count, int32_t dtype_dst,
+                                 void* stream) {
+  if (!ctx || !src || !dst || count < 0) return FRISK_B200_E_ARG;
+  FB_CUDA(ctx, cudaSetDevice(ctx->device));
+  return launch_convert_f32_clear(src, dst, count, dtype_dst, static_cast<cudaStream_t>(stream));
+}
+
+// ---- buffers other processes on this node can map (cudaIpc): the destinations of frisk_b200_gemm_push
+int frisk_b200_peer_buffer_create(frisk_b200_ctx* ctx, size_t bytes, void** ptr, void* handle64) {
+  if (!ctx || !ptr || !handle64 || bytes == 0) return FRISK_B200_E_ARG;
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle is 64 bytes");
+  FB_CUDA(ctx, cudaSetDevice(ctx->device));
+  void* p = nullptr;
+  FB_CUDA(ctx, cudaMalloc(&p, bytes));
+  cudaError_t e = cudaMemset(p, 0, bytes);
+  cudaIpcMemHandle_t h;
+  if (e == cudaSuccess) e = cudaIpcGetMemHandle(&h, p);
+  if (e != cudaSuccess) {
+    cudaFree(p);
+    ctx->last_cuda = (int)e;
+    return FRISK_B200_E_CUDA;
+  }
+  memcpy(handle64, &h, sizeof(h));
+  *ptr = p;
+  return 0;
+}
+int frisk_b200_peer_buffer_open(frisk_b200_ctx* ctx, const void* handle64, void** ptr) {
+  if (!ctx || !ptr || !handle64) return FRISK_B200_E_ARG;
+  FB_CUDA(ctx, cudaSetDevice(ctx->device));
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, sizeof(h));
+  FB_CUDA(ctx, cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess));
+  return 0;
+}
+int frisk_b200_peer_buffer_close(frisk_b200_ctx* ctx, void* ptr, int32_t owned) {
+  if (!ctx || !ptr) return FRISK_B200_E_ARG;
+  FB_CUDA(ctx, cudaSetDevice(ctx->device));
+  if (owned) FB_CUDA(ctx, cudaFree(ptr)); else FB_CUDA(ctx, cudaIpcCloseMemHandle(ptr));
   return 0;
 }
 

@@ -94,6 +94,12 @@ __device__ __forceinline__ void umma_f16_ss_pair(uint32_t tmem_d, uint64_t desc_
       ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// 16-byte fp32 reduction into global memory (local or a peer's): no return value, fire and forget
+__device__ __forceinline__ void red_add_v4(float* dst, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(__uint_as_float(a)),
+               "f"(__uint_as_float(b)), "f"(__uint_as_float(c)), "f"(__uint_as_float(d))
+               : "memory");
+}
 // arrive on the barrier at the same shared-memory offset in every CTA of `mask` once all MMAs
 // issued so far have completed
 __device__ __forceinline__ void umma_commit_pair(uint64_t* bar, uint16_t mask) {
@@ -122,7 +128,7 @@ __global__ void __launch_bounds__(kThreads2, 1)
     gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                              TO* __restrict__ C, int M, int N, int K, int64_t ldc, int accumulate, int vec_c,
                              int n_full, int n_items, float* __restrict__ partials,
-                             unsigned* __restrict__ tickets, unsigned* __restrict__ status) {
+                             unsigned* __restrict__ tickets, const PushTargets push, unsigned* __restrict__ status) {
   using L = Smem2;
   extern __shared__ unsigned char smem_unaligned[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(
@@ -320,7 +326,19 @@ __global__ void __launch_bounds__(kThreads2, 1)
             }
           }
           const int col = n0 + c * 32;
-          if (row < M && col < N)
+          if (push.n > 0) {
+            // split-K across GPUs: add this chunk into the buffer of the GPU that owns the row
+            if (row < M && col < N) {
+              const int owner = row / push.rows_per_target;
+              float* dst = push.ptr[owner] + (int64_t)(row - owner * push.rows_per_target) * push.ld + col;
+              if (col + 32 <= N && (push.ld & 3) == 0) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) red_add_v4(dst + 4 * i, v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+              } else {
+                for (int i = 0; i < 32 && col + i < N; ++i) atomicAdd(dst + i, __uint_as_float(v[i]));
+              }
+            }
+          } else if (row < M && col < N)
             store_row_chunk<TO>(C + (int64_t)row * ldc + col, v, min(32, N - col), vec_c != 0, accumulate != 0);
         }
       }
@@ -380,7 +398,7 @@ TailPlan make_tail_plan(const frisk_b200_gemm_desc& d, int pairs_available) {
 
 template <typename TO, bool BF16, bool A_MN, bool B_MN>
 int launch_cfg2(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc& d, const void* A, const void* B, void* C,
-                void* ws, size_t ws_bytes, cudaStream_t s) {
+                void* ws, size_t ws_bytes, cudaStream_t s, const PushTargets* push_in = nullptr) {
   GemmDims g = resolve_dims(d);
   CUtensorMap ta, tb;
   int rc;
@@ -414,7 +432,9 @@ int launch_cfg2(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc& d, const void* 
   if (max_clusters < 1) return FRISK_B200_E_UNSUPPORTED;
   if (max_clusters > kPairsAssumed) max_clusters = kPairsAssumed;
   TailPlan tp = make_tail_plan(d, max_clusters);
-  if (tp.bytes && (!ws || ws_bytes < tp.bytes)) {
+  PushTargets push{};
+  if (push_in) push = *push_in;
+  if (tp.bytes && (!ws || ws_bytes < tp.bytes || push.n > 0)) {
     // no scratch: run every tile whole
     tp.n_full = tp.n_items = tp.n_full + tp.tail_tiles;
     tp.tail_tiles = 0;
@@ -429,7 +449,7 @@ int launch_cfg2(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc& d, const void* 
   unsigned* st = ctx->d_status;
   int n_full = tp.n_full, n_items = tp.n_items;
   FB_CUDA(ctx, cudaLaunchKernelEx(&cfg, kern, ta, tb, Cp, Mi, Ni, Ki, ldc, acc, vec_c, n_full, n_items, partials,
-                                  tickets, st));
+                                  tickets, push, st));
   return 0;
 }
 
@@ -452,6 +472,18 @@ bool tcgen05_2cta_preferred(const frisk_b200_gemm_desc& d) {
   if (const char* e = getenv("FRISK_B200_GEMM_PAIR")) return e[0] == '1';
   const int64_t tiles = ((d.M + BM2 - 1) / BM2) * ((d.N + BN2 - 1) / BN2);
   return tiles >= kNumSMsDefault / 2;
+}
+
+// Split-K across GPUs: the same kernel, its epilogue adding every fp32 tile into the row owner's buffer.
+int launch_gemm_tcgen05_2cta_push(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc& d, const void* A, const void* B,
+                                  const PushTargets& push, cudaStream_t s) {
+  if (!tcgen05_supported(d) || d.dtype_c != FRISK_B200_F32) return FRISK_B200_E_UNSUPPORTED;
+  if (!aligned16(A) || !aligned16(B)) return FRISK_B200_E_ALIGN;
+  const bool a_mn = d.trans_a != 0, b_mn = d.trans_b == 0;
+  if (a_mn || b_mn) return FRISK_B200_E_UNSUPPORTED;  // the K-split path keeps both operands K-contiguous
+  if (d.dtype_ab == FRISK_B200_BF16)
+    return launch_cfg2<float, true, false, false>(ctx, d, A, B, nullptr, nullptr, 0, s, &push);
+  return launch_cfg2<float, false, false, false>(ctx, d, A, B, nullptr, nullptr, 0, s, &push);
 }
 
 // Worst case over the number of CTA pairs the device grants (at most kPairsAssumed/2 tail tiles).

@@ -144,3 +144,65 @@ class SplitKGemm:
         for p in range(max(0, plan.panels - len(self.partial)), plan.panels - 1):
             compute.wait_event(self.ev_comm[p])
         return self.out
+
+
+class SplitKGemmPush:
+    """The same K-split product with the exchange FUSED into the GEMM: the epilogue of the
+    tcgen05 kernel adds every finished fp32 tile straight into the memory of the GPU that owns
+    its rows (``frisk_b200_gemm_push``: 16-byte ``red.global.add`` over NVLink to buffers mapped
+    with cudaIpc), so the transfer overlaps the arithmetic tile by tile and no SM is taken away
+    by a collective kernel.  Rank r owns rows ``[r*M/g, (r+1)*M/g)``.
+
+    Per call: push; a one-element all-reduce on the stream as the cross-GPU barrier (every
+    rank's pushes are then complete); round this rank's rows to 16 bits and clear them.  Two
+    accumulation buffers alternate, so a rank that is already pushing call i+1 can never reach a
+    buffer its peer has not yet cleared after call i-1.  The additions arrive in no fixed
+    order: results are reproducible to fp32 rounding, not bit for bit."""
+
+    def __init__(self, M, N, K, world, rank, dtype, ctx, group=None):
+        import torch
+        import torch.distributed as dist
+        if M % world or K % world or (K // world) % 8 or world > 8:
+            raise ValueError("split-k push: M and K must divide by the number of ranks (<= 8)")
+        self.M, self.N, self.k_local, self.world, self.rank = M, N, K // world, world, rank
+        self.rows = M // world
+        self.ctx, self.group, self.dtype = ctx, group, dtype
+        self.device = torch.device("cuda", torch.cuda.current_device())
+        self.own, self.targets = [], []
+        for _ in range(2):
+            ptr, handle = ctx.peer_buffer_create(self.rows * N * 4)
+            handles = [None] * world
+            if world > 1:
+                dist.all_gather_object(handles, handle, group=group)
+            else:
+                handles = [handle]
+            self.own.append(ptr)
+            self.targets.append([ptr if r == rank else ctx.peer_buffer_open(handles[r]) for r in range(world)])
+        self.out = torch.empty(self.rows, N, dtype={"bf16": torch.bfloat16, "fp16": torch.float16}[dtype],
+                               device=self.device)
+        self.token = torch.zeros(1, device=self.device)
+        self.desc = capi.gemm_desc(M, N, self.k_local, dtype, "fp32", False, True, clear_accum=True,
+                                   algo=capi.ALGO_TCGEN05_PAIR)
+        self.calls = 0
+
+    def run(self, a_shard, b_shard):
+        """a_shard [M, K/g], b_shard [N, K/g] (K-contiguous).  Returns this rank's rows [M/g, N]."""
+        import torch
+        import torch.distributed as dist
+        if tuple(a_shard.shape) != (self.M, self.k_local) or tuple(b_shard.shape) != (self.N, self.k_local):
+            raise ValueError("split-k push: shard shapes do not match")
+        buf = self.calls & 1
+        self.calls += 1
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        self.ctx.gemm_push(self.desc, a_shard.data_ptr(), b_shard.data_ptr(), self.targets[buf], self.rows, self.N,
+                           stream=stream)
+        if self.world > 1:
+            dist.all_reduce(self.token, group=self.group)  # stream-ordered barrier across the GPUs
+        self.ctx.convert_f32_clear(self.own[buf], self.out.data_ptr(), self.rows * self.N, self.dtype, stream=stream)
+        return self.out
+
+    def close(self):
+        for buf in range(2):
+            for r, ptr in enumerate(self.targets[buf]):
+                self.ctx.peer_buffer_close(ptr, owned=(r == self.rank))
+        self.targets = []

@@ -249,3 +249,78 @@ def test_execute_bind_test_style(ctx):
     F.execute(mod, ta, tb, tc, torch.empty(512, dtype=torch.float16, device="cuda"))
     torch.cuda.synchronize()
     assert rel_frobenius(to_host(tc, "fp16"), gemm_oracle.gemm_fp64(a, b, "fp16")) <= TOL["fp16"]
+
+
+def test_gemm_push_into_row_block_owners(ctx):
+    """The fused split-K epilogue on one GPU: the fp32 product is added into two row-block
+    buffers (stand-ins for two GPUs' memories), twice, then rounded and cleared."""
+    import torch
+    M, N, K = 1024, 768, 512
+    a, b = inputs.gemm_inputs(M, N, K, "bf16", False, True, 61, "normal_rsqrt_k")
+    da, db = to_device(a, "bf16"), to_device(b, "bf16")
+    t0 = torch.zeros(M // 2, N, device="cuda")
+    t1 = torch.zeros(M // 2, N, device="cuda")
+    desc = capi.gemm_desc(M, N, K, "bf16", "fp32", False, True, clear_accum=True, algo=capi.ALGO_TCGEN05_PAIR)
+    s = torch.cuda.current_stream().cuda_stream
+    for _ in range(2):  # two ranks' worth of the same partial product
+        ctx.gemm_push(desc, da.data_ptr(), db.data_ptr(), [t0.data_ptr(), t1.data_ptr()], M // 2, N, stream=s)
+    ctx.check(s)
+    ref = 2.0 * gemm_oracle.gemm_fp64(a, b, "bf16", False, True)
+    got = torch.cat([t0, t1]).cpu().numpy()
+    assert rel_frobenius(got, ref) <= 1e-5
+    out = torch.empty(M // 2, N, dtype=torch.bfloat16, device="cuda")
+    ctx.convert_f32_clear(t1.data_ptr(), out.data_ptr(), out.numel(), "bf16", stream=s)
+    torch.cuda.synchronize()
+    assert rel_frobenius(from_storage(to_host(out, "bf16"), "bf16"), ref[M // 2:]) <= TOL["bf16"]
+    assert not t1.any()
+    with pytest.raises(ValueError):
+        ctx.gemm_push(desc, da.data_ptr(), db.data_ptr(), [t0.data_ptr()], M // 4, N, stream=s)  # rows not covered
+
+
+def _push_worker(rank, world, port, out_dir):
+    import os
+
+    import torch
+    import torch.distributed as dist
+
+    from frisk_b200 import splitk
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        c = capi.Context(rank)
+        M, N, K = 1024, 512, 2048
+        a, b = inputs.gemm_inputs(M, N, K, "bf16", False, True, 62, "normal_rsqrt_k")
+        kl = K // world
+        da = to_device(np.ascontiguousarray(a[:, rank * kl:(rank + 1) * kl]), "bf16", f"cuda:{rank}")
+        db = to_device(np.ascontiguousarray(b[:, rank * kl:(rank + 1) * kl]), "bf16", f"cuda:{rank}")
+        op = splitk.SplitKGemmPush(M, N, K, world, rank, "bf16", c, dist.group.WORLD)
+        for _ in range(3):
+            out = op.run(da, db)
+        torch.cuda.synchronize()
+        ref = gemm_oracle.gemm_fp64(a, b, "bf16", False, True)[rank * (M // world):(rank + 1) * (M // world)]
+        err = rel_frobenius(from_storage(to_host(out, "bf16"), "bf16"), ref)
+        with open(os.path.join(out_dir, f"err{rank}.txt"), "w") as f:
+            f.write(repr(err))
+        dist.barrier()
+        op.close()
+        c.close()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_splitk_push_two_gpus(tmp_path):
+    """Two ranks on two GPUs (skipped on a one-GPU box): each pushes its K half into the owners'
+    buffers over peer mappings; leaves between steps only, NVLS off."""
+    import socket
+
+    import torch
+    import torch.multiprocessing as mp
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    with socket.socket() as sk:
+        sk.bind(("127.0.0.1", 0))
+        port = sk.getsockname()[1]
+    mp.spawn(_push_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    for r in range(2):
+        assert float((tmp_path / f"err{r}.txt").read_text()) <= TOL["bf16"]
