@@ -283,7 +283,7 @@ __global__ void __launch_bounds__(kThreads2, 1)
       const uint32_t taddr = tmem_base + acc * BN2 + (static_cast<uint32_t>(quad * 32) << 16);
       bool write_c = true;
       const float4* other = nullptr;
-      if (it.tail >= 0) {
+      if (it.tail >= 0 && push.n == 0) {  // (pushed K halves simply both add into the owner's buffer)
         // leave this K half in the workspace, then see whether the other half is already there
         // scratch layout per (tail tile, K half, CTA): [64 groups of 4 columns][128 rows] float4, so that
         // the 32 lanes of a warp (32 consecutive rows) write and read consecutive 16-byte words
@@ -434,14 +434,14 @@ int launch_cfg2(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc& d, const void* 
   TailPlan tp = make_tail_plan(d, max_clusters);
   PushTargets push{};
   if (push_in) push = *push_in;
-  if (tp.bytes && (!ws || ws_bytes < tp.bytes || push.n > 0)) {
+  if (tp.bytes && push.n == 0 && (!ws || ws_bytes < tp.bytes)) {
     // no scratch: run every tile whole
     tp.n_full = tp.n_items = tp.n_full + tp.tail_tiles;
     tp.tail_tiles = 0;
   }
   cfg.gridDim = dim3(2 * tp.pairs);
   unsigned* tickets = static_cast<unsigned*>(ws);
-  float* partials = tp.tail_tiles ? reinterpret_cast<float*>(static_cast<unsigned char*>(ws) + tp.off_partials) : nullptr;
+  float* partials = (tp.tail_tiles && push.n == 0) ? reinterpret_cast<float*>(static_cast<unsigned char*>(ws) + tp.off_partials) : nullptr;
   int vec_c = aligned16(C) && (g.ldc * sizeof(TO)) % 16 == 0;
   TO* Cp = static_cast<TO*>(C);
   int Mi = (int)g.M, Ni = (int)g.N, Ki = (int)g.K, acc = d.clear_accum ? 0 : 1;

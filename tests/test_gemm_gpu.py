@@ -277,6 +277,21 @@ def test_gemm_push_into_row_block_owners(ctx):
         ctx.gemm_push(desc, da.data_ptr(), db.data_ptr(), [t0.data_ptr()], M // 4, N, stream=s)  # rows not covered
 
 
+def test_gemm_push_tail_wave_k_halves(ctx):
+    # 80 tiles on 74 CTA pairs: the last wave's tiles run as K halves that both add into the target
+    import torch
+    M, N, K = 2048, 2560, 512
+    a, b = inputs.gemm_inputs(M, N, K, "fp16", False, True, 63, "normal_rsqrt_k")
+    da, db = to_device(a, "fp16"), to_device(b, "fp16")
+    t = [torch.zeros(M // 4, N, device="cuda") for _ in range(4)]
+    desc = capi.gemm_desc(M, N, K, "fp16", "fp32", False, True, clear_accum=True, algo=capi.ALGO_TCGEN05_PAIR)
+    s = torch.cuda.current_stream().cuda_stream
+    ctx.gemm_push(desc, da.data_ptr(), db.data_ptr(), [x.data_ptr() for x in t], M // 4, N, stream=s)
+    ctx.check(s)
+    ref = gemm_oracle.gemm_fp64(a, b, "fp16", False, True)
+    assert rel_frobenius(torch.cat(t).cpu().numpy(), ref) <= 1e-5
+
+
 def _push_worker(rank, world, port, out_dir):
     import os
 
