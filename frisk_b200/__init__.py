@@ -6,7 +6,7 @@ attention path (``python/frisk/__init__.py:1-4``): the builder classes of
 ``attention_forward``, which run on the GPU through ``libfrisk_b200``.
 """
 from . import capi, ir
-from .execute import attention_forward, attention_geometry, execute, gemm, gemm_plan
+from .execute import attention_forward, attention_geometry, execute, fused_plan, gemm, gemm_plan
 from .helper import FriskHelper, create_context, create_session
 from .ir import (AffineMap, AllocBufferOp, BlockOp, CopyOp, FillOp, ForOp, GemmOp, GemmWarpPolicy, KernelOp,
                  MemorySpace, OpState, ParallelOp, ReduceOp, block, builder, context, frisk, module, type, value)

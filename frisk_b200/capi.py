@@ -27,6 +27,7 @@ EXPORTS = (
     "frisk_b200_attention_fwd_host", "frisk_b200_convert_f32", "frisk_b200_check",
     "frisk_b200_gemm_skinny_static", "frisk_b200_gemm_push", "frisk_b200_convert_f32_clear",
     "frisk_b200_peer_buffer_create", "frisk_b200_peer_buffer_open", "frisk_b200_peer_buffer_close",
+    "frisk_b200_gemm_fused_select", "frisk_b200_gemm_fused_workspace_bytes", "frisk_b200_gemm_fused",
 )
 
 
@@ -36,6 +37,28 @@ class GemmDesc(ctypes.Structure):
                 ("dtype_ab", ctypes.c_int32), ("dtype_c", ctypes.c_int32),
                 ("lda", ctypes.c_int64), ("ldb", ctypes.c_int64), ("ldc", ctypes.c_int64),
                 ("policy", ctypes.c_int32), ("algo", ctypes.c_int32)]
+
+
+class GemmEpilogue(ctypes.Structure):
+    _fields_ = [("fill_enable", ctypes.c_int32), ("fill_value", ctypes.c_float), ("reduce_kind", ctypes.c_int32),
+                ("reduce_clear", ctypes.c_int32), ("reduce_dst", ctypes.c_void_p)]
+
+
+REDUCE_KIND = {None: 0, "max": 1, "min": 2, "add": 3}
+
+
+def gemm_epilogue(fill=None, reduce=None, reduce_dst=None, reduce_clear=True):
+    """``fill``: value C was filled with right before an accumulating gemm; ``reduce``: kind of the
+    ``frisk.reduce`` along dim 1 right after it ('max' | 'min' | 'add'; 'mul' has no kernel)."""
+    if reduce not in REDUCE_KIND:
+        raise ValueError(f"frisk-b200: no kernel for reduce kind {reduce!r}")
+    e = GemmEpilogue()
+    e.fill_enable = 0 if fill is None else 1
+    e.fill_value = 0.0 if fill is None else float(fill)
+    e.reduce_kind = REDUCE_KIND[reduce]
+    e.reduce_clear = 1 if reduce_clear else 0
+    e.reduce_dst = reduce_dst
+    return e
 
 
 class AttnDesc(ctypes.Structure):
@@ -59,7 +82,7 @@ def load():
             "(there is no CPU fallback for the GEMM / attention kernels)")
     lib = ctypes.CDLL(os.fspath(path))
     vp, sz, i32, i64 = ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int32, ctypes.c_int64
-    gd, ad = ctypes.POINTER(GemmDesc), ctypes.POINTER(AttnDesc)
+    gd, ad, ge = ctypes.POINTER(GemmDesc), ctypes.POINTER(AttnDesc), ctypes.POINTER(GemmEpilogue)
     sig = {
         "frisk_b200_ctx_create": (ctypes.c_int, [ctypes.POINTER(vp), ctypes.c_int]),
         "frisk_b200_ctx_destroy": (ctypes.c_int, [vp]),
@@ -87,6 +110,9 @@ def load():
         "frisk_b200_peer_buffer_create": (ctypes.c_int, [vp, sz, ctypes.POINTER(vp), vp]),
         "frisk_b200_peer_buffer_open": (ctypes.c_int, [vp, vp, ctypes.POINTER(vp)]),
         "frisk_b200_peer_buffer_close": (ctypes.c_int, [vp, vp, i32]),
+        "frisk_b200_gemm_fused_select": (ctypes.c_int, [gd, ge]),
+        "frisk_b200_gemm_fused_workspace_bytes": (sz, [gd, ge]),
+        "frisk_b200_gemm_fused": (ctypes.c_int, [vp, gd, ge, vp, vp, vp, vp, sz, vp]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(lib, name)
@@ -158,6 +184,11 @@ class Context:
         rc = load().frisk_b200_gemm(self.handle, ctypes.byref(desc), a_ptr, b_ptr, c_ptr, ws_ptr, ws_bytes, stream)
         raise_for(rc, self._h)
 
+    def gemm_fused(self, desc, epi, a_ptr, b_ptr, c_ptr, ws_ptr=None, ws_bytes=0, stream=None):
+        rc = load().frisk_b200_gemm_fused(self.handle, ctypes.byref(desc), ctypes.byref(epi), a_ptr, b_ptr, c_ptr,
+                                          ws_ptr, ws_bytes, stream)
+        raise_for(rc, self._h)
+
     def gemm_host(self, desc, a_ptr, b_ptr, c_ptr):
         raise_for(load().frisk_b200_gemm_host(self.handle, ctypes.byref(desc), a_ptr, b_ptr, c_ptr), self._h)
 
@@ -200,6 +231,18 @@ class Context:
 
     def check(self, stream=None):
         raise_for(load().frisk_b200_check(self.handle, stream), self._h)
+
+
+def gemm_fused_select(desc, epi):
+    """1: fill / reduce run inside the GEMM epilogue; 0: composed from separate kernels.  Host-only."""
+    rc = load().frisk_b200_gemm_fused_select(ctypes.byref(desc), ctypes.byref(epi))
+    if rc < 0:
+        raise_for(rc)
+    return rc
+
+
+def gemm_fused_workspace_bytes(desc, epi):
+    return load().frisk_b200_gemm_fused_workspace_bytes(ctypes.byref(desc), ctypes.byref(epi))
 
 
 def gemm_check_memrefs(a_shape, a_dtype, b_shape, b_dtype, c_shape, c_dtype, trans_a, trans_b, m, n, k):

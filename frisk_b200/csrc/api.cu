@@ -586,6 +586,101 @@ int frisk_b200_gemm_push(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc* d, con
   return launch_gemm_tcgen05_2cta_push(ctx, *d, A, B, push, static_cast<cudaStream_t>(stream));
 }
 
+// ---- gemm with the fill / row-reduce that Frisk's IR places on the same C
+static int check_epilogue(const frisk_b200_gemm_desc* d, const frisk_b200_gemm_epilogue* e) {
+  if (!d || !e) return FRISK_B200_E_ARG;
+  int rc = frisk_b200_gemm_validate(d);
+  if (rc) return rc;
+  if (e->reduce_kind < FRISK_B200_REDUCE_NONE || e->reduce_kind > FRISK_B200_REDUCE_ADD) return FRISK_B200_E_UNSUPPORTED;
+  if (e->reduce_kind != FRISK_B200_REDUCE_NONE && !e->reduce_dst) return FRISK_B200_E_ARG;
+  if (!(e->fill_value == e->fill_value)) return FRISK_B200_E_ARG;  // NaN fill
+  return 0;
+}
+static float round_fill(float v, int dtype) {
+  if (dtype == FRISK_B200_F16) return __half2float(__float2half_rn(v));
+  if (dtype == FRISK_B200_BF16) return __bfloat162float(__float2bfloat16_rn(v));
+  return v;
+}
+int frisk_b200_gemm_fused_select(const frisk_b200_gemm_desc* d, const frisk_b200_gemm_epilogue* e) {
+  int rc = check_epilogue(d, e);
+  if (rc) return rc;
+  int algo = frisk_b200_gemm_select(d);
+  if (algo < 0) return algo;
+  if (algo != FRISK_B200_ALGO_TCGEN05_PAIR) return 0;
+  // a fused reduction needs the final value in registers: C must not be read back
+  if (e->reduce_kind != FRISK_B200_REDUCE_NONE && !d->clear_accum && !e->fill_enable) return 0;
+  return 1;
+}
+size_t frisk_b200_gemm_fused_workspace_bytes(const frisk_b200_gemm_desc* d, const frisk_b200_gemm_epilogue* e) {
+  int fused = frisk_b200_gemm_fused_select(d, e);
+  if (fused < 0) return 0;
+  size_t base = (frisk_b200_gemm_workspace_bytes(d) + 255) / 256 * 256;
+  if (fused == 1 && e->reduce_kind != FRISK_B200_REDUCE_NONE)
+    base += (size_t)tcgen05_2cta_column_tiles(*d) * (size_t)d->M * sizeof(float);
+  return base;
+}
+int frisk_b200_gemm_fused(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc* d, const frisk_b200_gemm_epilogue* e,
+                          const void* A, const void* B, void* C, void* workspace, size_t workspace_bytes,
+                          void* stream) {
+  if (!ctx || !A || !B || !C) return FRISK_B200_E_ARG;
+  int fused = frisk_b200_gemm_fused_select(d, e);
+  if (fused < 0) return fused;
+  GemmExtents ext = gemm_extents(*d);
+  GemmDims g = resolve_dims(*d);
+  const size_t cs = dtype_size(d->dtype_c);
+  if (ranges_overlap(C, ext.c, A, ext.a) || ranges_overlap(C, ext.c, B, ext.b)) return FRISK_B200_E_OVERLAP;
+  if (e->reduce_kind != FRISK_B200_REDUCE_NONE &&
+      (ranges_overlap(e->reduce_dst, (size_t)g.M * cs, C, ext.c) || ranges_overlap(e->reduce_dst, (size_t)g.M * cs, A, ext.a) ||
+       ranges_overlap(e->reduce_dst, (size_t)g.M * cs, B, ext.b)))
+    return FRISK_B200_E_OVERLAP;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  FB_CUDA(ctx, cudaSetDevice(ctx->device));
+  const bool use_fill = e->fill_enable && !d->clear_accum;  // a fill before an overwriting gemm is dead
+  const float fill = round_fill(e->fill_value, d->dtype_c);
+  if (fused == 0) {
+    int rc = 0;
+    if (use_fill && (rc = launch_fill(C, g.M, g.N, g.ldc, fill, d->dtype_c, s))) return rc;
+    if ((rc = frisk_b200_gemm(ctx, d, A, B, C, workspace, workspace_bytes, stream))) return rc;
+    if (e->reduce_kind != FRISK_B200_REDUCE_NONE)
+      rc = launch_row_reduce(C, g.M, g.N, g.ldc, e->reduce_kind, e->reduce_clear, e->reduce_dst, d->dtype_c, s);
+    return rc;
+  }
+  const size_t tail = (tcgen05_2cta_workspace_bytes(*d) + 255) / 256 * 256;
+  const int tiles_n = tcgen05_2cta_column_tiles(*d);
+  const size_t part = e->reduce_kind != FRISK_B200_REDUCE_NONE ? (size_t)tiles_n * (size_t)g.M * sizeof(float) : 0;
+  void* ws_tail = workspace;
+  float* ws_part = nullptr;
+  size_t ws_tail_bytes = 0;
+  if (workspace) {
+    if (workspace_bytes < tail + part) return FRISK_B200_E_WORKSPACE;
+    ws_tail_bytes = tail;
+    ws_part = reinterpret_cast<float*>(static_cast<unsigned char*>(workspace) + tail);
+  } else {
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    int rc;
+    if (tail) {
+      if ((rc = ensure_stage(ctx, 5, tail, true))) return rc;
+      ws_tail = ctx->stage[5].ptr;
+      ws_tail_bytes = ctx->stage[5].bytes;
+    }
+    if (part) {
+      if ((rc = ensure_stage(ctx, 6, part, false))) return rc;
+      ws_part = static_cast<float*>(ctx->stage[6].ptr);
+    }
+  }
+  if (!tail) ws_tail = nullptr;
+  EpilogueArgs ea{};
+  ea.has_fill = use_fill ? 1 : 0;
+  ea.fill = fill;
+  ea.reduce_kind = e->reduce_kind;
+  ea.row_partials = ws_part;
+  int rc = launch_gemm_tcgen05_2cta(ctx, *d, A, B, C, ws_tail, ws_tail_bytes, s, &ea);
+  if (rc) return rc;
+  if (e->reduce_kind != FRISK_B200_REDUCE_NONE)
+    rc = launch_row_finalize(ws_part, tiles_n, g.M, e->reduce_kind, e->reduce_clear, e->reduce_dst, d->dtype_c, s);
+  return rc;
+}
+
 int frisk_b200_convert_f32_clear(frisk_b200_ctx* ctx, float* src, void* dst, int64_t count, int32_t dtype_dst,
                                  void* stream) {
   if (!ctx || !src || !dst || count < 0) return FRISK_B200_E_ARG;

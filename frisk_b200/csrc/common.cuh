@@ -35,7 +35,7 @@ struct frisk_b200_ctx {
   unsigned* d_status = nullptr;  // device status word (first failing wait records its code)
   unsigned* h_status = nullptr;  // pinned mirror
   // staging for the *_host entry points and library-owned workspace
-  fb::StagingBuffer stage[6];  // 0-2 A/B/C staging, 3 skinny scratch, 4 V staging, 5 GEMM tail scratch
+  fb::StagingBuffer stage[7];  // 0-2 A/B/C staging, 3 skinny scratch, 4 V staging, 5 GEMM tail scratch, 6 row partials
   cudaStream_t host_stream = nullptr;
   cudaStream_t copy_stream = nullptr;
   cudaStream_t out_stream = nullptr;
@@ -96,6 +96,14 @@ struct PushTargets {
   int rows_per_target;
   int64_t ld;            // row pitch of every destination, in elements
 };
+// What the pair kernel does with a finished tile besides storing it (frisk.fill before, frisk.reduce
+// along dim 1 after the gemm, on the same C).
+struct EpilogueArgs {
+  int has_fill;         // C_in is the constant `fill`; C is not read
+  float fill;           // already rounded to C's element type
+  int reduce_kind;      // FRISK_B200_REDUCE_*; over the ROUNDED values that are stored
+  float* row_partials;  // [column tiles of 256][M] fp32, one partial per (tile column, row)
+};
 bool tcgen05_2cta_preferred(const frisk_b200_gemm_desc& d);
 int launch_gemm_tcgen05_2cta_push(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc& d, const void* A, const void* B,
                                   const PushTargets& push, cudaStream_t s);
@@ -103,7 +111,14 @@ int launch_convert_f32_clear(float* src, void* dst, int64_t n, int dtype, cudaSt
 // scratch for the K-split tail wave (0 when every tile runs whole); tickets at its start must be zero
 size_t tcgen05_2cta_workspace_bytes(const frisk_b200_gemm_desc& d);
 int launch_gemm_tcgen05_2cta(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc& d, const void* A, const void* B,
-                             void* C, void* ws, size_t ws_bytes, cudaStream_t s);
+                             void* C, void* ws, size_t ws_bytes, cudaStream_t s, const EpilogueArgs* epi = nullptr);
+int tcgen05_2cta_column_tiles(const frisk_b200_gemm_desc& d);
+// epilogue.cu
+int launch_row_finalize(const float* partials, int tiles_n, int64_t M, int kind, int clear, void* dst, int dtype,
+                        cudaStream_t s);
+int launch_row_reduce(const void* C, int64_t M, int64_t N, int64_t ldc, int kind, int clear, void* dst, int dtype,
+                      cudaStream_t s);
+int launch_fill(void* C, int64_t M, int64_t N, int64_t ldc, float value, int dtype, cudaStream_t s);
 
 int launch_attention_fwd(frisk_b200_ctx* ctx, const frisk_b200_attn_desc& d, const void* Q, const void* K,
                          const void* V, void* O, cudaStream_t s);

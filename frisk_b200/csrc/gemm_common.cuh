@@ -19,6 +19,16 @@ __device__ __forceinline__ TileCoord tile_coord(int t, int tiles_m, int tiles_n)
   return TileCoord{first_m + r % gsize, r / gsize};
 }
 
+// the value an fp32 result takes once it is stored as TO
+template <typename TO>
+__device__ __forceinline__ float rounded_as(float v);
+template <>
+__device__ __forceinline__ float rounded_as<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float rounded_as<__half>(float v) { return __half2float(__float2half_rn(v)); }
+template <>
+__device__ __forceinline__ float rounded_as<__nv_bfloat16>(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+
 template <typename TO>
 __device__ __forceinline__ void store_row_chunk(TO* p, const uint32_t (&v)[32], int valid, bool vec_ok,
                                                 bool accumulate);

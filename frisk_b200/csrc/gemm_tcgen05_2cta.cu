@@ -128,7 +128,8 @@ __global__ void __launch_bounds__(kThreads2, 1)
     gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                              TO* __restrict__ C, int M, int N, int K, int64_t ldc, int accumulate, int vec_c,
                              int n_full, int n_items, float* __restrict__ partials,
-                             unsigned* __restrict__ tickets, const PushTargets push, unsigned* __restrict__ status) {
+                             unsigned* __restrict__ tickets, const PushTargets push, const EpilogueArgs epi,
+                             unsigned* __restrict__ status) {
   using L = Smem2;
   extern __shared__ unsigned char smem_unaligned[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(
@@ -309,6 +310,8 @@ __global__ void __launch_bounds__(kThreads2, 1)
         epi_sync();  // everybody has read the ticket before the next item overwrites it
         if (write_c && warp == 2 && lane == 0) tickets[it.tail * 2 + rank] = 0;
       }
+      float row_acc = epi.reduce_kind == FRISK_B200_REDUCE_MAX ? -INFINITY
+                      : epi.reduce_kind == FRISK_B200_REDUCE_MIN ? INFINITY : 0.f;
       if (write_c) {
 #pragma unroll 1
         for (int c = 0; c < BN2 / 32; ++c) {
@@ -338,9 +341,27 @@ __global__ void __launch_bounds__(kThreads2, 1)
                 for (int i = 0; i < 32 && col + i < N; ++i) atomicAdd(dst + i, __uint_as_float(v[i]));
               }
             }
-          } else if (row < M && col < N)
-            store_row_chunk<TO>(C + (int64_t)row * ldc + col, v, min(32, N - col), vec_c != 0, accumulate != 0);
+          } else if (row < M && col < N) {
+            const int valid = min(32, N - col);
+            if (epi.has_fill) {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) + epi.fill);
+            }
+            store_row_chunk<TO>(C + (int64_t)row * ldc + col, v, valid, vec_c != 0, accumulate != 0);
+            if (epi.reduce_kind) {
+              // over the values as they were stored (accumulate is off whenever a reduction is fused)
+#pragma unroll
+              for (int i = 0; i < 32; ++i) {
+                const float r = rounded_as<TO>(__uint_as_float(v[i]));
+                if (i < valid)
+                  row_acc = epi.reduce_kind == FRISK_B200_REDUCE_MAX   ? fmaxf(row_acc, r)
+                            : epi.reduce_kind == FRISK_B200_REDUCE_MIN ? fminf(row_acc, r)
+                                                                       : row_acc + r;
+              }
+            }
+          }
         }
+        if (epi.reduce_kind && row < M) epi.row_partials[(int64_t)tc.n * M + row] = row_acc;
       }
       tc_fence_before_sync();
       __syncwarp();
@@ -398,7 +419,8 @@ TailPlan make_tail_plan(const frisk_b200_gemm_desc& d, int pairs_available) {
 
 template <typename TO, bool BF16, bool A_MN, bool B_MN>
 int launch_cfg2(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc& d, const void* A, const void* B, void* C,
-                void* ws, size_t ws_bytes, cudaStream_t s, const PushTargets* push_in = nullptr) {
+                void* ws, size_t ws_bytes, cudaStream_t s, const PushTargets* push_in = nullptr,
+                const EpilogueArgs* epi_in = nullptr) {
   GemmDims g = resolve_dims(d);
   CUtensorMap ta, tb;
   int rc;
@@ -434,6 +456,8 @@ int launch_cfg2(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc& d, const void* 
   TailPlan tp = make_tail_plan(d, max_clusters);
   PushTargets push{};
   if (push_in) push = *push_in;
+  EpilogueArgs epi{};
+  if (epi_in) epi = *epi_in;
   if (tp.bytes && push.n == 0 && (!ws || ws_bytes < tp.bytes)) {
     // no scratch: run every tile whole
     tp.n_full = tp.n_items = tp.n_full + tp.tail_tiles;
@@ -444,25 +468,25 @@ int launch_cfg2(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc& d, const void* 
   float* partials = (tp.tail_tiles && push.n == 0) ? reinterpret_cast<float*>(static_cast<unsigned char*>(ws) + tp.off_partials) : nullptr;
   int vec_c = aligned16(C) && (g.ldc * sizeof(TO)) % 16 == 0;
   TO* Cp = static_cast<TO*>(C);
-  int Mi = (int)g.M, Ni = (int)g.N, Ki = (int)g.K, acc = d.clear_accum ? 0 : 1;
+  int Mi = (int)g.M, Ni = (int)g.N, Ki = (int)g.K, acc = (d.clear_accum || epi.has_fill) ? 0 : 1;
   int64_t ldc = g.ldc;
   unsigned* st = ctx->d_status;
   int n_full = tp.n_full, n_items = tp.n_items;
   FB_CUDA(ctx, cudaLaunchKernelEx(&cfg, kern, ta, tb, Cp, Mi, Ni, Ki, ldc, acc, vec_c, n_full, n_items, partials,
-                                  tickets, push, st));
+                                  tickets, push, epi, st));
   return 0;
 }
 
 template <typename TO, bool BF16>
 int launch_major2(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc& d, const void* A, const void* B, void* C,
-                  void* ws, size_t ws_bytes, cudaStream_t s) {
+                  void* ws, size_t ws_bytes, cudaStream_t s, const EpilogueArgs* epi) {
   bool a_mn = d.trans_a != 0, b_mn = d.trans_b == 0;
   if (a_mn) {
-    if (b_mn) return launch_cfg2<TO, BF16, true, true>(ctx, d, A, B, C, ws, ws_bytes, s);
-    return launch_cfg2<TO, BF16, true, false>(ctx, d, A, B, C, ws, ws_bytes, s);
+    if (b_mn) return launch_cfg2<TO, BF16, true, true>(ctx, d, A, B, C, ws, ws_bytes, s, nullptr, epi);
+    return launch_cfg2<TO, BF16, true, false>(ctx, d, A, B, C, ws, ws_bytes, s, nullptr, epi);
   }
-  if (b_mn) return launch_cfg2<TO, BF16, false, true>(ctx, d, A, B, C, ws, ws_bytes, s);
-  return launch_cfg2<TO, BF16, false, false>(ctx, d, A, B, C, ws, ws_bytes, s);
+  if (b_mn) return launch_cfg2<TO, BF16, false, true>(ctx, d, A, B, C, ws, ws_bytes, s, nullptr, epi);
+  return launch_cfg2<TO, BF16, false, false>(ctx, d, A, B, C, ws, ws_bytes, s, nullptr, epi);
 }
 
 }  // namespace
@@ -486,6 +510,8 @@ int launch_gemm_tcgen05_2cta_push(frisk_b200_ctx* ctx, const frisk_b200_gemm_des
   return launch_cfg2<float, false, false, false>(ctx, d, A, B, nullptr, nullptr, 0, s, &push);
 }
 
+int tcgen05_2cta_column_tiles(const frisk_b200_gemm_desc& d) { return (int)((resolve_dims(d).N + BN2 - 1) / BN2); }
+
 // Worst case over the number of CTA pairs the device grants (at most kPairsAssumed/2 tail tiles).
 size_t tcgen05_2cta_workspace_bytes(const frisk_b200_gemm_desc& d) {
   GemmDims g = resolve_dims(d);
@@ -495,15 +521,15 @@ size_t tcgen05_2cta_workspace_bytes(const frisk_b200_gemm_desc& d) {
 }
 
 int launch_gemm_tcgen05_2cta(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc& d, const void* A, const void* B,
-                             void* C, void* ws, size_t ws_bytes, cudaStream_t s) {
+                             void* C, void* ws, size_t ws_bytes, cudaStream_t s, const EpilogueArgs* epi) {
   if (!tcgen05_supported(d)) return FRISK_B200_E_UNSUPPORTED;
   if (!aligned16(A) || !aligned16(B)) return FRISK_B200_E_ALIGN;
   const bool bf = d.dtype_ab == FRISK_B200_BF16;
   if (d.dtype_c == FRISK_B200_F32)
-    return bf ? launch_major2<float, true>(ctx, d, A, B, C, ws, ws_bytes, s)
-              : launch_major2<float, false>(ctx, d, A, B, C, ws, ws_bytes, s);
-  if (bf) return launch_major2<__nv_bfloat16, true>(ctx, d, A, B, C, ws, ws_bytes, s);
-  return launch_major2<__half, false>(ctx, d, A, B, C, ws, ws_bytes, s);
+    return bf ? launch_major2<float, true>(ctx, d, A, B, C, ws, ws_bytes, s, epi)
+              : launch_major2<float, false>(ctx, d, A, B, C, ws, ws_bytes, s, epi);
+  if (bf) return launch_major2<__nv_bfloat16, true>(ctx, d, A, B, C, ws, ws_bytes, s, epi);
+  return launch_major2<__half, false>(ctx, d, A, B, C, ws, ws_bytes, s, epi);
 }
 
 }  // namespace fb

@@ -8,7 +8,9 @@ pattern-matched on the host and dispatched through the C ABI of ``libfrisk_b200`
 
 * a kernel whose only computation is one ``frisk.gemm`` over its global memref
   arguments, possibly nested in ``frisk.parallel`` / ``frisk.block`` / ``frisk.for``
-  (tile shapes there are scheduling hints; the hand-written kernels fix their own);
+  (tile shapes there are scheduling hints; the hand-written kernels fix their own),
+  optionally with a ``frisk.fill`` of C before it and a ``frisk.reduce`` of C along dim 1
+  after it, which run inside the GEMM's epilogue;
 * the attention-forward graph, entered through :func:`attention_forward` with the
   launch contract of ``tiled_attention.py:28-61`` (compact BHSD, spec dict B/H/N/D).
 
@@ -48,8 +50,11 @@ def _stream_ptr(stream, device):
 
 
 def _find_gemm(kernel):
-    """Return (gemm_op, enclosing_ops) or raise ValueError naming what is unsupported."""
-    found = []
+    """Return (gemm_op, enclosing_ops, fill_op or None, reduce_op or None) or raise ValueError naming
+    what is unsupported.  Besides the structural ops, the kernel may hold a ``frisk.fill`` of the
+    gemm's C before the gemm and a ``frisk.reduce`` of C along dim 1 after it, in program order
+    (the neighbours ``test/python/bind_test.py:44-53`` gives a gemm); they become the GEMM's epilogue."""
+    found, order = [], []
 
     def visit(op, chain):
         for r in op.regions:
@@ -57,17 +62,35 @@ def _find_gemm(kernel):
                 for child in b.operations:
                     if isinstance(child, ir.GemmOp):
                         found.append((child, chain))
+                        order.append(child)
+                    elif isinstance(child, (ir.FillOp, ir.ReduceOp)):
+                        order.append(child)
                     elif isinstance(child, (ir.ParallelOp, ir.BlockOp, ir.ForOp)):
                         visit(child, chain + [child])
                     elif isinstance(child, (ir.AllocBufferOp, ir.EndOp)):
                         continue
                     else:
-                        raise ValueError(f"frisk-b200-execute: unsupported op {child.op_name} in an executed kernel")
+                        order.append(child)
 
     visit(kernel, [])
     if len(found) != 1:
         raise ValueError(f"frisk-b200-execute: expected exactly one frisk.gemm, found {len(found)}")
-    return found[0]
+    gemm, chain = found[0]
+    c_val = gemm.operands[2]
+    at = order.index(gemm)
+    fill = reduce = None
+    for pos, op in enumerate(order):  # the first offender in program order is the one reported
+        if op is gemm:
+            continue
+        if isinstance(op, ir.FillOp) and op.operands[0] is c_val and pos < at and fill is None:
+            fill = op
+        elif isinstance(op, ir.ReduceOp) and op.operands[0] is c_val and pos > at and reduce is None \
+                and op.attrs["dim"] == 1:
+            reduce = op
+        else:
+            raise ValueError(f"frisk-b200-execute: unsupported op {op.op_name} in an executed kernel"
+                             " (besides the gemm: one fill of its C before it, one reduce of its C along dim 1 after it)")
+    return gemm, chain, fill, reduce
 
 
 def _kernel_of(module_or_kernel, name=None):
@@ -81,13 +104,14 @@ def _kernel_of(module_or_kernel, name=None):
     return kernels[0]
 
 
-def gemm_plan(module_or_kernel, name=None, algo=capi.ALGO_AUTO):
-    """Host-only: resolve the kernel to (descriptor, (ia, ib, ic)) where the indices name the
-    kernel arguments bound to A, B and C."""
+def fused_plan(module_or_kernel, name=None, algo=capi.ALGO_AUTO):
+    """Host-only: resolve the kernel to (descriptor, (ia, ib, ic), epilogue) where the indices name
+    the kernel arguments bound to A, B and C and ``epilogue`` is None or a dict with ``fill``
+    (value or None), ``reduce`` (kind or None), ``reduce_arg`` (argument index) and ``reduce_clear``."""
     kernel = _kernel_of(module_or_kernel, name)
     if not kernel.verify():
         raise ValueError("frisk-b200-execute: kernel does not verify")
-    gemm, chain = _find_gemm(kernel)
+    gemm, chain, fill, reduce = _find_gemm(kernel)
     entry = kernel.regions[0].front()
     idx = []
     for v in gemm.operands:
@@ -97,7 +121,8 @@ def gemm_plan(module_or_kernel, name=None, algo=capi.ALGO_AUTO):
             raise ValueError("frisk-b200-execute: gemm operands must be global memrefs")
         idx.append(v.index)
     a = gemm.attrs
-    if not a["clear_accum"]:
+    side = fill is not None or reduce is not None
+    if not a["clear_accum"] or side:
         trips = 1
         for op in chain:
             if isinstance(op, ir.ForOp):
@@ -111,14 +136,34 @@ def gemm_plan(module_or_kernel, name=None, algo=capi.ALGO_AUTO):
     desc = capi.gemm_desc(a["M"], a["N"], a["K"], code[ta.element.name], code[tc.element.name],
                           a["transA"], a["transB"], a["clear_accum"], algo=algo)
     desc.policy = int(a["policy"])
-    return desc, tuple(idx)
+    epilogue = None
+    if side:
+        epilogue = {"fill": None, "reduce": None, "reduce_arg": None, "reduce_clear": True}
+        if fill is not None:
+            epilogue["fill"] = fill.attrs["value"][0]
+        if reduce is not None:
+            dst = reduce.operands[1]
+            if not (dst.is_arg and dst.owner is entry) or dst.type.space != ir.MemorySpace.GLOBAL:
+                raise ValueError("frisk-b200-execute: the reduce destination must be a global kernel argument")
+            if reduce.attrs["kind"] not in ("max", "min", "add"):
+                raise ValueError(f"frisk-b200-execute: no kernel for reduce kind {reduce.attrs['kind']}")
+            epilogue.update(reduce=reduce.attrs["kind"], reduce_arg=dst.index, reduce_clear=bool(reduce.attrs["clear"]))
+    return desc, tuple(idx), epilogue
+
+
+def gemm_plan(module_or_kernel, name=None, algo=capi.ALGO_AUTO):
+    """Host-only: resolve a kernel whose only computation is one gemm to (descriptor, (ia, ib, ic))."""
+    desc, idx, epilogue = fused_plan(module_or_kernel, name, algo)
+    if epilogue is not None:
+        raise ValueError("frisk-b200-execute: the kernel holds a fill or reduce next to its gemm: use fused_plan")
+    return desc, idx
 
 
 def execute(module_or_kernel, *tensors, stream=None, name=None, algo=capi.ALGO_AUTO):
     """Run the kernel on CUDA tensors bound positionally to its memref arguments."""
     torch = _torch()
     kernel = _kernel_of(module_or_kernel, name)
-    desc, (ia, ib, ic) = gemm_plan(kernel, algo=algo)
+    desc, (ia, ib, ic), epilogue = fused_plan(kernel, algo=algo)
     arg_types = kernel.attrs["function_type"].inputs
     if len(tensors) != len(arg_types):
         raise ValueError(f"frisk-b200-execute: kernel takes {len(arg_types)} tensors, got {len(tensors)}")
@@ -135,7 +180,14 @@ def execute(module_or_kernel, *tensors, stream=None, name=None, algo=capi.ALGO_A
     a, b, c = tensors[ia], tensors[ib], tensors[ic]
     dev = c.device.index or 0
     ctx = context_for(dev)
-    ctx.gemm(desc, a.data_ptr(), b.data_ptr(), c.data_ptr(), stream=_stream_ptr(stream, c.device))
+    if epilogue is None:
+        ctx.gemm(desc, a.data_ptr(), b.data_ptr(), c.data_ptr(), stream=_stream_ptr(stream, c.device))
+    else:
+        dst = tensors[epilogue["reduce_arg"]] if epilogue["reduce"] else None
+        epi = capi.gemm_epilogue(fill=epilogue["fill"], reduce=epilogue["reduce"],
+                                 reduce_dst=dst.data_ptr() if dst is not None else None,
+                                 reduce_clear=epilogue["reduce_clear"])
+        ctx.gemm_fused(desc, epi, a.data_ptr(), b.data_ptr(), c.data_ptr(), stream=_stream_ptr(stream, c.device))
     return c
 
 

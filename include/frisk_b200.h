@@ -198,6 +198,43 @@ int frisk_b200_convert_f32(frisk_b200_ctx* ctx, const float* src, void* dst, int
 int frisk_b200_gemm_push(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc* desc, const void* A,
                          const void* B, float* const* targets, int32_t n_targets,
                          int64_t rows_per_target, int64_t ld_target, void* stream);
+/* ---- what Frisk's IR can put next to a gemm on the same C --------------------------------
+ * `frisk.fill` of C directly before an accumulating gemm and `frisk.reduce` of C along dim 1
+ * directly after it (builders ffi/ir.cpp:439-456 and 457-470; ops
+ * include/Dialect/Frisk/IR/FriskOps.td:400-423 and 425-453, reduce contract
+ * lib/Dialect/Frisk/IR/FriskOps.cpp:728-762; the flow of test/python/bind_test.py:44-53).
+ * frisk_b200_gemm_fused computes
+ *     C <- (fill_enable ? fill_value : clear_accum ? 0 : C) + op(A).op(B)
+ *     reduce_dst[i] <- (reduce_clear ? identity : reduce_dst[i]) (+) reduce_j C[i][j]
+ * with the reduction taken over the values of C as stored (rounded to its element type) and
+ * accumulated in fp32.  On the tcgen05 pair kernel both happen in the GEMM's epilogue (C is
+ * not read for the fill; the reduction costs one fp32 per row and 256 columns, combined in a
+ * fixed order); for the other kernels, and for a reduction after an accumulate that reads C,
+ * the same result is produced by a fill kernel before and a row-reduction kernel after the
+ * GEMM.  Kind `mul` of the reference has no kernel here (FRISK_B200_E_UNSUPPORTED). */
+enum {
+  FRISK_B200_REDUCE_NONE = 0,
+  FRISK_B200_REDUCE_MAX = 1,
+  FRISK_B200_REDUCE_MIN = 2,
+  FRISK_B200_REDUCE_ADD = 3
+};
+typedef struct frisk_b200_gemm_epilogue {
+  int32_t fill_enable;  /* C holds fill_value everywhere (it need not have been written) */
+  float fill_value;     /* rounded to C's element type before use, as frisk.fill stores it */
+  int32_t reduce_kind;  /* FRISK_B200_REDUCE_* */
+  int32_t reduce_clear; /* 1: overwrite reduce_dst; 0: combine with what it holds */
+  void* reduce_dst;     /* M elements of C's element type; may be NULL when reduce_kind is NONE */
+} frisk_b200_gemm_epilogue;
+/* 1 when the descriptor/epilogue pair runs fused in the GEMM epilogue, 0 when it is composed
+ * from separate kernels, negative error code otherwise.  Host-only. */
+int frisk_b200_gemm_fused_select(const frisk_b200_gemm_desc* desc, const frisk_b200_gemm_epilogue* epi);
+size_t frisk_b200_gemm_fused_workspace_bytes(const frisk_b200_gemm_desc* desc,
+                                             const frisk_b200_gemm_epilogue* epi);
+/* workspace may be NULL: the context then owns the scratch (allocated on first use). */
+int frisk_b200_gemm_fused(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc* desc,
+                          const frisk_b200_gemm_epilogue* epi, const void* A, const void* B, void* C,
+                          void* workspace, size_t workspace_bytes, void* stream);
+
 /* Round an fp32 buffer to 16 bits and zero it in the same pass (ready for the next push). */
 int frisk_b200_convert_f32_clear(frisk_b200_ctx* ctx, float* src, void* dst, int64_t count,
                                  int32_t dtype_dst, void* stream);

@@ -81,3 +81,22 @@ def gemm_f32_blas(a_store, b_store, dtype_ab, trans_a=False, trans_b=False):
     a = from_storage(a_store, dtype_ab)
     b = from_storage(b_store, dtype_ab)
     return (a.T if trans_a else a) @ (b.T if trans_b else b)
+
+
+def row_reduce(c_storage, dtype_c, kind, dst_init=None):
+    """``frisk.reduce`` of C along dim 1 (lib/Dialect/Frisk/IR/FriskOps.cpp:728-762): over the values
+    of C as stored, combined in fp64 (exact for max/min), optionally with the destination's
+    earlier contents (clear = false).  Returns fp64, not rounded."""
+    c = from_storage(c_storage, dtype_c).astype(np.float64)
+    if kind == "max":
+        r = c.max(axis=1)
+    elif kind == "min":
+        r = c.min(axis=1)
+    elif kind == "add":
+        r = c.sum(axis=1)
+    else:
+        raise ValueError(f"unsupported reduce kind: {kind}. Supported: add, mul, min, max")
+    if dst_init is not None:
+        d = from_storage(dst_init, dtype_c).astype(np.float64)
+        r = np.maximum(r, d) if kind == "max" else np.minimum(r, d) if kind == "min" else r + d
+    return r

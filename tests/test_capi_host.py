@@ -1,9 +1,12 @@
 """Host-only checks of the C ABI: the library loads, exports every symbol the header
 declares, and its contract checks agree with the oracle's restatement of
 LegacyImportSemantics.cpp:11-46.  No compute call is made here."""
+import ctypes
 import itertools
 import pathlib
 import re
+
+import pytest
 
 from frisk_b200 import capi
 from oracle import gemm_oracle
@@ -86,3 +89,27 @@ def test_attention_validate():
     assert lib.frisk_b200_attention_validate(capi.attn_desc(1, 1, 64, 64, 64, 0.1, False, "fp32")) == -6
     assert lib.frisk_b200_attention_validate(capi.attn_desc(1, 1, 128, 64, 64, 0.1, True, "fp16")) == -8
     assert lib.frisk_b200_attention_validate(capi.attn_desc(1, 1, 64, 64, 64, 0.125, False, "fp16", "fp32")) == 0
+
+
+def test_fused_epilogue_selection_and_workspace():
+    """Host-only: when fill / reduce run inside the GEMM epilogue and how much scratch that takes."""
+    big = capi.gemm_desc(4096, 4096, 4096, "fp16", "fp16", False, True, clear_accum=True)
+    small = capi.gemm_desc(256, 256, 256, "fp16", "fp16", False, True, clear_accum=True)
+    f32 = capi.gemm_desc(1024, 1024, 1024, "fp32", "fp32")
+    red = capi.gemm_epilogue(reduce="max", reduce_dst=0x1000)
+    assert capi.gemm_fused_select(big, red) == 1
+    assert capi.gemm_fused_select(small, red) == 0
+    assert capi.gemm_fused_select(f32, red) == 0
+    acc = capi.gemm_desc(4096, 4096, 4096, "fp16", "fp16", False, True, clear_accum=False)
+    assert capi.gemm_fused_select(acc, red) == 0                                        # C is read back
+    assert capi.gemm_fused_select(acc, capi.gemm_epilogue(fill=1.0, reduce="add", reduce_dst=0x1000)) == 1
+    assert capi.gemm_fused_select(acc, capi.gemm_epilogue(fill=1.0)) == 1
+    base = capi.load().frisk_b200_gemm_workspace_bytes(ctypes.byref(big))
+    assert capi.gemm_fused_workspace_bytes(big, red) == (base + 255) // 256 * 256 + 16 * 4096 * 4
+    assert capi.gemm_fused_workspace_bytes(small, red) == 0
+    with pytest.raises(ValueError):
+        capi.gemm_epilogue(reduce="mul")                        # the reference's fourth kind has no kernel
+    with pytest.raises(ValueError):
+        capi.gemm_fused_select(big, capi.gemm_epilogue(reduce="max"))   # no destination
+    with pytest.raises(ValueError):
+        capi.gemm_fused_select(big, capi.gemm_epilogue(fill=float("nan")))

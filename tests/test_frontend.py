@@ -156,3 +156,49 @@ def test_execute_refuses_cpu_tensors():
     v = torch.zeros(128, dtype=torch.float16)
     with pytest.raises(ValueError, match="no CPU path"):
         F.execute(mod, t, t, t.clone(), v)
+
+
+def build_fused_module(fill=None, reduce=None, clear=True, clear_accum=False, shape=(512, 384, 256), trips=1):
+    """kernel(A[M,K], B[N,K], C[M,N], r[M]): parallel { for { [fill C] gemm(A, B^T, C) [reduce C -> r] } }"""
+    m, n, k = shape
+    context = F.context()
+    F.frisk.load_dialects(context)
+    builder = F.builder(context)
+    module = builder.create_module()
+    module.context = context
+    f16 = builder.get_f16_ty()
+    types = [builder.get_memref_ty(f16, s, F.AffineMap(), F.MemorySpace.GLOBAL) for s in ([m, k], [n, k], [m, n], [m])]
+    kernel = builder.create_kernel_op(module, "fused", builder.get_kernel_ty(types))
+    module.push_back(kernel)
+    entry = kernel.add_entry_block()
+    builder.set_insertion_point_to_start(entry)
+    par = builder.create_parallel_op([4, 4], 128)
+    builder.set_insertion_point_to_start(par.add_entry_block())
+    a, b, c, r = (entry.get_argument(i) for i in range(4))
+
+    def body(bld, iv):
+        if fill is not None:
+            builder.create_fill_op(c, fill, "fp16")
+        builder.create_gemm_op(a, b, c, False, True, clear_accum)
+        if reduce is not None:
+            builder.create_reduce_op(c, r, reduce, 1, clear)
+    builder.create_for_op(0, trips, 1, body)
+    return module
+
+
+def test_fused_plan_folds_fill_and_reduce_into_the_gemm():
+    desc, idx, epi = F.fused_plan(build_fused_module(fill=0.5, reduce="max", clear=False))
+    assert (desc.M, desc.N, desc.K, desc.trans_b, desc.clear_accum) == (512, 384, 256, 1, 0) and idx == (0, 1, 2)
+    assert epi == {"fill": 0.5, "reduce": "max", "reduce_arg": 3, "reduce_clear": False}
+    _, _, epi = F.fused_plan(build_fused_module(reduce="add", clear_accum=True))
+    assert epi == {"fill": None, "reduce": "add", "reduce_arg": 3, "reduce_clear": True}
+    assert F.fused_plan(build_fused_module(clear_accum=True))[2] is None
+    with pytest.raises(ValueError, match="use fused_plan"):
+        F.gemm_plan(build_fused_module(fill=1.0))
+    with pytest.raises(ValueError, match="no kernel for reduce kind mul"):
+        F.fused_plan(build_fused_module(reduce="mul", clear_accum=True))
+    with pytest.raises(ValueError, match="multi-trip"):
+        F.fused_plan(build_fused_module(fill=1.0, trips=3))
+    # a fill or reduce that does not touch the gemm's C stays unsupported (the bind_test neighbours)
+    with pytest.raises(ValueError, match="unsupported op frisk.fill"):
+        F.fused_plan(build_bind_test_module(clear_accum=True, with_side_ops=True))

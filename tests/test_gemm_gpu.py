@@ -339,3 +339,104 @@ def test_splitk_push_two_gpus(tmp_path):
     mp.spawn(_push_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
     for r in range(2):
         assert float((tmp_path / f"err{r}.txt").read_text()) <= TOL["bf16"]
+
+
+# ------------------------------------------------------------------ fill / row-reduce next to the gemm
+def run_fused(ctx, M, N, K, dtype_ab, dtype_c, seed, *, fill=None, kind=None, clear=True, clear_accum=True,
+              algo=capi.ALGO_AUTO, c_init=None, expect_fused=None):
+    """-> (C storage, reduce storage or None, oracle C fp64, r_init)."""
+    import torch
+    a, b = inputs.gemm_inputs(M, N, K, dtype_ab, False, True, seed, "normal_rsqrt_k")
+    ga, gb = Guarded(a.shape, dtype_ab, fill=a), Guarded(b.shape, dtype_ab, fill=b)
+    gc = Guarded((M, N), dtype_c, fill=c_init)
+    if c_init is None:
+        gc.view.fill_(float("nan"))  # must not be read: neither with clear_accum nor with a fill
+    rng = np.random.default_rng(seed + 7)
+    r_init = to_storage(rng.standard_normal(M, dtype=np.float32), dtype_c)
+    gr = Guarded((M,), dtype_c, fill=r_init)
+    desc = capi.gemm_desc(M, N, K, dtype_ab, dtype_c, False, True, clear_accum=clear_accum, algo=algo)
+    epi = capi.gemm_epilogue(fill=fill, reduce=kind, reduce_dst=gr.view.data_ptr() if kind else None,
+                             reduce_clear=clear)
+    if expect_fused is not None:
+        assert capi.gemm_fused_select(desc, epi) == expect_fused
+    s = torch.cuda.current_stream().cuda_stream
+    ctx.gemm_fused(desc, epi, ga.view.data_ptr(), gb.view.data_ptr(), gc.view.data_ptr(), stream=s)
+    ctx.check(s)
+    assert gc.guards_intact() and gr.guards_intact()
+    base = None
+    if fill is not None and not clear_accum:
+        base = np.broadcast_to(to_storage(np.float32(fill).reshape(1, 1), dtype_c), (M, N))
+    elif not clear_accum:
+        base = c_init
+    ref = gemm_oracle.gemm_fp64(a, b, dtype_ab, False, True, base, dtype_c)
+    return gc.host(), (gr.host() if kind else None), ref, r_init
+
+
+def check_reduce(got_c, got_r, dtype_c, kind, clear, r_init):
+    want = gemm_oracle.row_reduce(got_c, dtype_c, kind, None if clear else r_init)
+    got = from_storage(got_r, dtype_c).astype(np.float64)
+    if kind == "add":  # fp32 accumulation, one rounding to the element type
+        assert np.all(np.abs(got - want) <= 2e-3 * np.abs(want) + 2e-2)
+    else:              # exact: the extreme of the stored values
+        assert np.array_equal(got, want)
+
+
+@pytest.mark.parametrize("dtype_c", ["fp16", "fp32"])
+@pytest.mark.parametrize("kind", ["max", "min", "add"])
+def test_fused_row_reduce_in_pair_epilogue(ctx, kind, dtype_c):
+    # 9 x 10 tiles on 74 pairs: whole tiles and a K-split tail wave; ragged N masks the last columns
+    for N, clear in ((2560, True), (2496, False)):
+        c, r, ref, r0 = run_fused(ctx, 2304, N, 512, "fp16", dtype_c, 70, kind=kind, clear=clear, expect_fused=1)
+        assert rel_frobenius(from_storage(c, dtype_c), ref) <= TOL["fp16"]
+        check_reduce(c, r, dtype_c, kind, clear, r0)
+
+
+def test_fused_fill_replaces_the_read_of_c(ctx):
+    # C holds NaN: a fused fill must not read it.  bf16 output, then with a reduction on top.
+    c, _, ref, _ = run_fused(ctx, 2304, 2560, 256, "bf16", "bf16", 71, fill=0.75, clear_accum=False, expect_fused=1)
+    assert rel_frobenius(from_storage(c, "bf16"), ref) <= TOL["bf16"]
+    c, r, ref, r0 = run_fused(ctx, 2304, 2560, 256, "bf16", "bf16", 72, fill=-1.5, kind="max", clear_accum=False,
+                              expect_fused=1)
+    assert rel_frobenius(from_storage(c, "bf16"), ref) <= TOL["bf16"]
+    check_reduce(c, r, "bf16", "max", True, r0)
+
+
+def test_fill_and_reduce_composed_for_the_other_kernels(ctx):
+    # one-CTA tcgen05 kernel, fp32 SIMT kernel, skinny kernel, and a reduction after an accumulate that reads C
+    c, r, ref, r0 = run_fused(ctx, 384, 520, 192, "fp16", "fp16", 73, fill=0.25, kind="add", clear_accum=False,
+                              clear=False, expect_fused=0)
+    assert rel_frobenius(from_storage(c, "fp16"), ref) <= TOL["fp16"]
+    check_reduce(c, r, "fp16", "add", False, r0)
+    c, r, ref, r0 = run_fused(ctx, 130, 77, 51, "fp32", "fp32", 74, kind="min", expect_fused=0)
+    assert rel_frobenius(c, ref) <= TOL["fp32"]
+    check_reduce(c, r, "fp32", "min", True, r0)
+    c, r, ref, r0 = run_fused(ctx, 8, 4096, 1024, "bf16", "bf16", 75, kind="max", expect_fused=0)
+    assert rel_frobenius(from_storage(c, "bf16"), ref) <= TOL["bf16"]
+    check_reduce(c, r, "bf16", "max", True, r0)
+    rng = np.random.default_rng(76)
+    c0 = to_storage(rng.standard_normal((2304, 2560), dtype=np.float32), "fp16")
+    c, r, ref, r0 = run_fused(ctx, 2304, 2560, 256, "fp16", "fp16", 76, kind="max", clear_accum=False, c_init=c0,
+                              expect_fused=0)
+    assert rel_frobenius(from_storage(c, "fp16"), ref) <= TOL["fp16"]
+    check_reduce(c, r, "fp16", "max", True, r0)
+
+
+def test_execute_kernel_with_fill_and_reduce(ctx):
+    """The builder flow end to end: fill C, gemm, reduce C along dim 1, run through ``execute``."""
+    import torch
+
+    import frisk_b200 as F
+    from tests.test_frontend import build_fused_module
+    M, N, K = 512, 384, 256
+    a, b = inputs.gemm_inputs(M, N, K, "fp16", False, True, 77, "normal_rsqrt_k")
+    ta, tb = to_device(a, "fp16"), to_device(b, "fp16")
+    tc = torch.full((M, N), float("nan"), dtype=torch.float16, device="cuda")
+    tr = torch.zeros(M, dtype=torch.float16, device="cuda")
+    F.execute(build_fused_module(fill=0.5, reduce="max"), ta, tb, tc, tr)
+    torch.cuda.synchronize()
+    base = np.full((M, N), np.float16(0.5))
+    ref = gemm_oracle.gemm_fp64(a, b, "fp16", False, True, base, "fp16")
+    got = to_host(tc, "fp16")
+    assert rel_frobenius(from_storage(got, "fp16"), ref) <= TOL["fp16"]
+    assert np.array_equal(from_storage(to_host(tr, "fp16"), "fp16").astype(np.float64),
+                          gemm_oracle.row_reduce(got, "fp16", "max"))
