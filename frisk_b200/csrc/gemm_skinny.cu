@@ -8,31 +8,41 @@
 //   in shared memory (16 x K/S elements, rows padded by 64 bytes so that the fragment
 //   reads below are bank-conflict free).
 // * A warp owns one group of 8 weight rows at a time, taken from a per-split queue in the
-//   workspace (an atomic counter), so all warps stay busy to the end of the stream; the
-//   loads of the next 256-wide k chunk (or of the next row group) are issued before the
-//   current chunk is multiplied.
-// * Each lane loads 16 bytes (8 consecutive k) of "its" weight row.  Because a dot product
-//   does not care about the order of k, those 8 values feed two m16n8k16 tensor-core MMAs
-//   directly as B fragments, with the matching 8 values of X rows g and g+8 as A
-//   fragments: no shuffles, no shared-memory staging of W.
-// * With S > 1 a warp writes its fp32 16x8 partial to the workspace, takes a ticket for the
-//   row group, and the warp that draws the last ticket adds the S partials in split order
-//   (deterministic) and writes the rounded output.
+//   workspace (an atomic counter), so all warps stay busy to the end of the stream.
+// * HBM under load answers after 2-3 us, so ~128 KB per SM must be in flight to keep it busy:
+//   more than registers can hold.  Each warp therefore streams its rows with cp.async (16
+//   bytes per lane, one instruction = 512 contiguous bytes of one row, zero-filled past the
+//   end of the slice) into a private ring of five 4 KB slots in shared memory and keeps four
+//   256-wide k chunks in flight while it multiplies the oldest one.
+// * The MMA wants lane (g, t) to supply row g.  Because a dot product does not care about the
+//   order of k, the lane simply reads 16 bytes (8 consecutive k) of row g back from the slot
+//   and feeds two m16n8k16 tensor-core MMAs with them as B fragments, with the matching 8
+//   values of X rows g and g+8 as A fragments.  16-byte pieces are XOR-swizzled with the row
+//   so that neither the cp.async writes nor these reads have bank conflicts.
+// * With S > 1 a warp leaves its fp32 16x8 partial in the workspace and moves on (no fence, no
+//   ticket: either would stall the warp's stream for a microsecond per row group); a second,
+//   tiny kernel adds the S partials in split order (deterministic) and writes the rounded
+//   output.  The id of the next row group is requested from the queue one chunk before it is
+//   needed, so the atomic's round trip is hidden as well.
 // All control words are left at zero when the kernel ends.
 #include "common.cuh"
 
 namespace fb {
 namespace {
 
-constexpr int kThreads = 512;
+constexpr int kThreads = 256;
 constexpr int kWarps = kThreads / 32;
-constexpr int kUnroll = 8;               // 16-byte weight loads in flight per lane
+constexpr int kUnroll = 8;               // k steps per chunk = rows per group
+constexpr int kDepth = 5;                // ring slots per warp (kDepth - 1 chunks in flight)
 constexpr int kStepK = 32;               // k covered by one warp step (4 lanes x 8 elements)
 constexpr int kChunkK = kStepK * kUnroll;  // 256
 constexpr int kRowPadBytes = 64;
 constexpr int kCtlInts = 64;             // ctr[0..31], done = [32]
 constexpr int kMaxSplit = 32;
-constexpr size_t kMaxSmem = 200 * 1024;
+constexpr int kSlotBytes = 8 * kChunkK * 2;                            // 8 rows x 512 bytes
+constexpr int kRingBytes = kWarps * kDepth * kSlotBytes;               // 160 KB
+constexpr int kFifoBytes = kWarps * 8 * 4;
+constexpr size_t kMaxSmem = 232448 - 1024;                             // X slice + rings + fifos
 
 struct SkinnyPlan {
   int S;            // K splits
@@ -42,14 +52,6 @@ struct SkinnyPlan {
   size_t off_tickets, off_partials, ws_bytes;
   int grid;
 };
-
-__device__ __forceinline__ uint4 ldg_stream(const void* p) {
-  uint4 v;
-  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(p));
-  return v;
-}
 
 template <typename T>
 __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -90,6 +92,23 @@ __device__ __forceinline__ float from_f32<float>(float v) { return v; }
 template <>
 __device__ __forceinline__ float to_f32<float>(float v) { return v; }
 
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ uint4 lds_v4(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "r"(addr)
+               : "memory");
+  return v;
+}
+
 // TO = output element type (T or float)
 template <typename T, typename TO>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -97,135 +116,142 @@ __global__ void __launch_bounds__(kThreads, 1)
                        int K, int64_t ldx, int64_t ldw, int64_t ldy, int S, int kslice, int ngroups,
                        int accumulate, unsigned* __restrict__ ctl, unsigned* __restrict__ tickets,
                        float* __restrict__ partials) {
-  extern __shared__ __align__(16) unsigned char smem_raw[];
-  const int tid = threadIdx.x, lane = tid & 31;
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t = lane & 3;
   const int s = blockIdx.x % S;
   const int kbeg = s * kslice;
   const int klen = max(0, min(K, kbeg + kslice) - kbeg);  // valid k in this slice (multiple of 8)
   const int pitch = kslice * (int)sizeof(T) + kRowPadBytes;
 
-  // ---- stage this split's slice of X (rows >= M and k beyond the slice are zero)
-  {
-    const int vec_per_row = kslice / 8;
-    for (int i = tid; i < 16 * vec_per_row; i += kThreads) {
-      int r = i / vec_per_row, kv = (i % vec_per_row) * 8;
-      uint4 v = make_uint4(0, 0, 0, 0);
-      if (r < M && kv < klen) v = __ldg(reinterpret_cast<const uint4*>(X + (int64_t)r * ldx + kbeg + kv));
-      *reinterpret_cast<uint4*>(smem_raw + (size_t)r * pitch + (size_t)kv * sizeof(T)) = v;
-    }
-  }
-  __syncthreads();
-
   const unsigned char* xs_lo = smem_raw + (size_t)g * pitch + (size_t)t * 8 * sizeof(T);
   const unsigned char* xs_hi = xs_lo + (size_t)8 * pitch;
   const int Npad = ngroups * 8;
+  // this warp's ring of weight chunks and its queue of row groups in flight
+  const uint32_t ring = static_cast<uint32_t>(__cvta_generic_to_shared(smem_raw)) + 16u * (uint32_t)pitch +
+                        (uint32_t)(warp * kDepth) * kSlotBytes;
+  volatile unsigned* fifo = reinterpret_cast<volatile unsigned*>(smem_raw + (size_t)16 * pitch + kRingBytes) + warp * 8;
+  const int nchunks = (klen + kChunkK - 1) / kChunkK;
 
-  auto grab = [&]() -> unsigned {
-    unsigned v = 0;
-    if (lane == 0) v = atomicAdd(&ctl[s], 1u);
-    return __shfl_sync(0xffffffffu, v, 0);
+  // the queue: lane 0 requests an id early (the atomic's result is not touched until it is taken)
+  unsigned requested = 0;
+  auto request = [&]() {
+    if (lane == 0) requested = atomicAdd(&ctl[s], 1u);
   };
-  auto row_ptr = [&](unsigned group) -> const T* {
-    const int n_row = min((int)group * 8 + g, N - 1);
-    return W + (int64_t)n_row * ldw + kbeg + t * 8;
-  };
-  auto load_chunk = [&](uint4 (&w)[kUnroll], const T* wrow, int k0) {
-#pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
-      int kk = k0 + u * kStepK + t * 8;
-      w[u] = (kk < klen) ? ldg_stream(wrow + k0 + u * kStepK) : make_uint4(0, 0, 0, 0);
+  auto take = [&]() -> unsigned { return __shfl_sync(0xffffffffu, requested, 0); };
+
+  if (nchunks > 0) {
+    // ---- issue side: runs kDepth - 1 chunks ahead of the multiplication
+    request();
+    unsigned ng_issue = take(), pushed = 0;
+    int c_issue = 0, slot_issue = 0;
+    bool issue_live = ng_issue < (unsigned)ngroups;
+    if (issue_live) {
+      if (lane == 0) fifo[pushed & 7] = ng_issue;
+      ++pushed;
     }
-  };
-
-  // Software pipeline over (row group, 256-wide k chunk) items: the weight loads of the next
-  // item -- which may belong to the next row group -- are in flight while the current
-  // item is multiplied, so a warp always has 8..16 16-byte loads outstanding.
-  unsigned ng = grab();
-  if (ng < (unsigned)ngroups) {
-    int k0 = 0;
-    const T* wrow = row_ptr(ng);
-    uint4 wc[kUnroll];
-    load_chunk(wc, wrow, k0);
-    float acc0[4] = {0.f, 0.f, 0.f, 0.f}, acc1[4] = {0.f, 0.f, 0.f, 0.f};
-    while (true) {
-      unsigned ng_n = ng;
-      int k0_n = k0 + kChunkK;
-      if (k0_n >= klen) {
-        ng_n = grab();
-        k0_n = 0;
+    auto issue_one = [&]() {
+      if (issue_live) {
+        const int k0 = c_issue * kChunkK + lane * 8;      // this lane's 16-byte piece
+        const int bytes = k0 < klen ? 16 : 0;              // 0: the destination is zero-filled
+        const T* src = W + kbeg + min(k0, klen - 8);
+        const uint32_t dst = ring + (uint32_t)slot_issue * kSlotBytes;
+        if (c_issue == nchunks - 1) request();  // answered while this chunk streams in
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {                // u = row within the group
+          const int n_row = min((int)ng_issue * 8 + u, N - 1);
+          cp_async16(dst + u * (kChunkK * 2) + (((lane ^ (u << 2)) & 31) << 4), src + (int64_t)n_row * ldw, bytes);
+        }
+        if (++c_issue == nchunks) {
+          c_issue = 0;
+          ng_issue = take();
+          issue_live = ng_issue < (unsigned)ngroups;
+          if (issue_live) {
+            if (lane == 0) fifo[pushed & 7] = ng_issue;
+            ++pushed;
+          }
+        }
       }
-      const bool have_next = ng_n < (unsigned)ngroups;
-      const T* wrow_n = have_next ? (k0_n == 0 ? row_ptr(ng_n) : wrow) : wrow;
-      uint4 wn[kUnroll];
-      if (have_next) load_chunk(wn, wrow_n, k0_n);
+      cp_async_commit();  // also when nothing was issued: the group count stays in step
+      slot_issue = slot_issue + 1 == kDepth ? 0 : slot_issue + 1;
+    };
+#pragma unroll
+    for (int d = 0; d < kDepth - 1; ++d) issue_one();
 
+    // ---- stage this split's slice of X (rows >= M and k beyond the slice are zero) while the first
+    // weight chunks are already on their way
+    {
+      const int vec_per_row = kslice / 8;
+      for (int i = tid; i < 16 * vec_per_row; i += kThreads) {
+        int r = i / vec_per_row, kv = (i % vec_per_row) * 8;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (r < M && kv < klen) v = __ldg(reinterpret_cast<const uint4*>(X + (int64_t)r * ldx + kbeg + kv));
+        *reinterpret_cast<uint4*>(smem_raw + (size_t)r * pitch + (size_t)kv * sizeof(T)) = v;
+      }
+    }
+    __syncthreads();
+
+    // ---- multiplication side
+    unsigned popped = 0;
+    int c = 0, slot = 0;
+    float acc0[4] = {0.f, 0.f, 0.f, 0.f}, acc1[4] = {0.f, 0.f, 0.f, 0.f};
+    while (popped < pushed) {
+      issue_one();                 // refills the slot that was multiplied in the previous round
+      cp_async_wait<kDepth - 1>();  // everything but the newest kDepth - 1 chunks has landed
+      __syncwarp();
+      const unsigned ng = fifo[popped & 7];
+      const uint32_t base = ring + (uint32_t)slot * kSlotBytes + (uint32_t)g * (kChunkK * 2);
+      const int k0 = c * kChunkK;
 #pragma unroll
       for (int u = 0; u < kUnroll; ++u) {
         size_t off = (size_t)(k0 + u * kStepK) * sizeof(T);
         uint4 xa = *reinterpret_cast<const uint4*>(xs_lo + off);
         uint4 xb = *reinterpret_cast<const uint4*>(xs_hi + off);
-        mma16816<T>(acc0, xa.x, xb.x, xa.y, xb.y, wc[u].x, wc[u].y);
-        mma16816<T>(acc1, xa.z, xb.z, xa.w, xb.w, wc[u].z, wc[u].w);
+        const uint4 w = lds_v4(base + ((((u << 2) + t) ^ (g << 2)) << 4));
+        mma16816<T>(acc0, xa.x, xb.x, xa.y, xb.y, w.x, w.y);
+        mma16816<T>(acc1, xa.z, xb.z, xa.w, xb.w, w.z, w.w);
       }
+      __syncwarp();  // every lane is done with the slot before it is refilled
+      slot = slot + 1 == kDepth ? 0 : slot + 1;
+      if (++c < nchunks) continue;
+      c = 0;
+      ++popped;
 
-      if (k0_n == 0) {  // the current row group is complete
-        float c[4];
+      // ---- the row group is complete
+      float cc4[4];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          c[i] = acc0[i] + acc1[i];
-          acc0[i] = 0.f;
-          acc1[i] = 0.f;
-        }
-        const int col = (int)ng * 8 + 2 * t;  // output columns col, col+1 ; rows g and g+8
-        bool write_out = true;
-        if (S > 1) {
-          float* pp = partials + ((size_t)s * 16 + g) * Npad + col;
-          __stcg(reinterpret_cast<float2*>(pp), make_float2(c[0], c[1]));
-          __stcg(reinterpret_cast<float2*>(pp + (size_t)8 * Npad), make_float2(c[2], c[3]));
-          __threadfence();
-          __syncwarp();
-          unsigned ticket = 0;
-          if (lane == 0) ticket = atomicAdd(&tickets[ng], 1u);
-          ticket = __shfl_sync(0xffffffffu, ticket, 0);
-          write_out = ticket == (unsigned)(S - 1);
-          if (write_out) {
-            __threadfence();
-            c[0] = c[1] = c[2] = c[3] = 0.f;
-            for (int ss = 0; ss < S; ++ss) {
-              const float* qq = partials + ((size_t)ss * 16 + g) * Npad + col;
-              float2 lo = __ldcg(reinterpret_cast<const float2*>(qq));
-              float2 hi = __ldcg(reinterpret_cast<const float2*>(qq + (size_t)8 * Npad));
-              c[0] += lo.x; c[1] += lo.y; c[2] += hi.x; c[3] += hi.y;
-            }
-            if (lane == 0) tickets[ng] = 0;
-          }
-        }
-        if (write_out) {
+      for (int i = 0; i < 4; ++i) {
+        cc4[i] = acc0[i] + acc1[i];
+        acc0[i] = 0.f;
+        acc1[i] = 0.f;
+      }
+      const int col = (int)ng * 8 + 2 * t;  // output columns col, col+1 ; rows g and g+8
+      if (S > 1) {
+        float* pp = partials + ((size_t)s * 16 + g) * Npad + col;
+        __stcg(reinterpret_cast<float2*>(pp), make_float2(cc4[0], cc4[1]));
+        __stcg(reinterpret_cast<float2*>(pp + (size_t)8 * Npad), make_float2(cc4[2], cc4[3]));
+        continue;
+      }
+      {
 #pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            int r = g + 8 * h;
-            if (r >= M) continue;
+        for (int h = 0; h < 2; ++h) {
+          int r = g + 8 * h;
+          if (r >= M) continue;
 #pragma unroll
-            for (int jj = 0; jj < 2; ++jj) {
-              int cc = col + jj;
-              if (cc >= N) continue;
-              TO* y = Y + (int64_t)r * ldy + cc;
-              float v = c[2 * h + jj];
-              if (accumulate) v += to_f32<TO>(*y);
-              *y = from_f32<TO>(v);
-            }
+          for (int jj = 0; jj < 2; ++jj) {
+            int cc = col + jj;
+            if (cc >= N) continue;
+            TO* y = Y + (int64_t)r * ldy + cc;
+            float v = cc4[2 * h + jj];
+            if (accumulate) v += to_f32<TO>(*y);
+            *y = from_f32<TO>(v);
           }
         }
       }
-      if (!have_next) break;
-      ng = ng_n;
-      k0 = k0_n;
-      wrow = wrow_n;
-#pragma unroll
-      for (int u = 0; u < kUnroll; ++u) wc[u] = wn[u];
     }
+    cp_async_wait<0>();
   }
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // the reduction grid may be scheduled
 
   // ---- leave the queue counters at zero for the next launch
   __syncthreads();
@@ -240,13 +266,39 @@ __global__ void __launch_bounds__(kThreads, 1)
   }
 }
 
+// Y[r][n] = (accumulate ? Y[r][n] : 0) + sum over the splits, in split order, of partials[s][r][n]
+template <typename TO>
+__global__ void __launch_bounds__(256) skinny_reduce_kernel(const float* __restrict__ partials, int S, int Npad,
+                                                            int M, int N, TO* __restrict__ Y, int64_t ldy,
+                                                            int accumulate) {
+  const int n = (blockIdx.x * 256 + threadIdx.x) * 2;
+  const int r = blockIdx.y;
+  // launched with programmatic stream serialization: the grid may be resident before the
+  // streaming kernel has ended; its partial sums are visible after this wait
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  if (n >= N || r >= M) return;
+  float2 acc = make_float2(0.f, 0.f);
+  for (int ss = 0; ss < S; ++ss) {
+    const float2 v = __ldcg(reinterpret_cast<const float2*>(partials + ((size_t)ss * 16 + r) * Npad + n));
+    acc.x += v.x;
+    acc.y += v.y;
+  }
+  TO* y = Y + (int64_t)r * ldy + n;
+  if (accumulate) acc.x += to_f32<TO>(y[0]);
+  y[0] = from_f32<TO>(acc.x);
+  if (n + 1 < N) {
+    if (accumulate) acc.y += to_f32<TO>(y[1]);
+    y[1] = from_f32<TO>(acc.y);
+  }
+}
+
 SkinnyPlan make_plan(const frisk_b200_gemm_desc& d, int num_sms) {
   SkinnyPlan p{};
   size_t es = dtype_size(d.dtype_ab);
   p.ngroups = (int)((d.N + 7) / 8);
   int S = 1;
   auto slice_of = [&](int s) { return (int)(((d.K + s - 1) / s + kChunkK - 1) / kChunkK * kChunkK); };
-  auto smem_of = [&](int s) { return (size_t)16 * ((size_t)slice_of(s) * es + kRowPadBytes); };
+  auto smem_of = [&](int s) { return (size_t)16 * ((size_t)slice_of(s) * es + kRowPadBytes) + kRingBytes + kFifoBytes; };
   while (S < kMaxSplit && smem_of(S) > kMaxSmem) ++S;
   // enough warp-sized work items to keep every warp of the machine busy a few times over
   long want_items = (long)num_sms * kWarps * 4;
@@ -284,6 +336,22 @@ int launch_typed(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc& d, const Skinn
                                         reinterpret_cast<unsigned*>(w + p.off_tickets),
                                         reinterpret_cast<float*>(w + p.off_partials));
   FB_CUDA(ctx, cudaGetLastError());
+  if (p.S > 1) {
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.gridDim = dim3((unsigned)((p.ngroups * 8 / 2 + 255) / 256), (unsigned)g.M);
+    cfg.blockDim = dim3(256);
+    cfg.stream = s;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const float* parts = reinterpret_cast<const float*>(w + p.off_partials);
+    int Sv = p.S, Npad = p.ngroups * 8, Mi = (int)g.M, Ni = (int)g.N, acc = d.clear_accum ? 0 : 1;
+    TO* Yp = static_cast<TO*>(C);
+    int64_t ldy = g.ldc;
+    FB_CUDA(ctx, cudaLaunchKernelEx(&cfg, skinny_reduce_kernel<TO>, parts, Sv, Npad, Mi, Ni, Yp, ldy, acc));
+  }
   return 0;
 }
 
@@ -339,7 +407,7 @@ int launch_gemm_skinny(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc& d, const
 namespace fb {
 namespace {
 
-constexpr size_t kStaticScratchBytes = 8u << 20;  // 8 MiB: the 16 x 28672 x 8192 decode GEMM needs 5.3 MiB
+constexpr size_t kStaticScratchBytes = 8u << 20;  // 8 MiB: the 16 x 28672 x 8192 decode GEMM needs 7.0 MiB
 constexpr int kMaxDevices = 64;
 
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];

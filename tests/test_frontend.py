@@ -202,3 +202,30 @@ def test_fused_plan_folds_fill_and_reduce_into_the_gemm():
     # a fill or reduce that does not touch the gemm's C stays unsupported (the bind_test neighbours)
     with pytest.raises(ValueError, match="unsupported op frisk.fill"):
         F.fused_plan(build_bind_test_module(clear_accum=True, with_side_ops=True))
+
+
+REFERENCE_TESTS = "/root/reference/test/python"
+
+
+@pytest.mark.parametrize("script", ["bind_test.py", "helper_test.py", "test.py"])
+def test_reference_builder_scripts_run_verbatim(script, capsys):
+    """The reference's own builder scripts (`import frisk as F`), unmodified, against this
+    package under the name `frisk`.  Skipped where the reference checkout is not present."""
+    import os
+    import runpy
+    import sys
+    path = os.path.join(REFERENCE_TESTS, script)
+    if not os.path.exists(path):
+        pytest.skip("reference checkout not present")
+    saved = sys.modules.get("frisk")
+    sys.modules["frisk"] = F
+    try:
+        runpy.run_path(path, run_name="__main__")
+    finally:
+        if saved is None:
+            sys.modules.pop("frisk", None)
+        else:
+            sys.modules["frisk"] = saved
+    out = capsys.readouterr().out
+    if script == "bind_test.py":
+        assert "frisk.gemm" in out and "frisk.reduce" in out and "frisk.fill" in out
