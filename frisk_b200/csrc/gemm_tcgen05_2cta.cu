@@ -123,7 +123,11 @@ __device__ __forceinline__ Item2 get_item2(int i, int n_full, int num_kb) {
   return Item2{n_full + tail, half ? mid : 0, half ? num_kb : mid, tail, half};
 }
 
-template <typename TO, bool BF16, bool A_MN, bool B_MN>
+// MODE: what the epilogue does with a finished tile.  Separate instantiations, so that the plain
+// store keeps its register budget and code exactly as if the other two did not exist.
+enum { kStore = 0, kPush = 1, kFused = 2 };
+
+template <typename TO, bool BF16, bool A_MN, bool B_MN, int MODE>
 __global__ void __launch_bounds__(kThreads2, 1)
     gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                              TO* __restrict__ C, int M, int N, int K, int64_t ldc, int accumulate, int vec_c,
@@ -284,7 +288,7 @@ __global__ void __launch_bounds__(kThreads2, 1)
       const uint32_t taddr = tmem_base + acc * BN2 + (static_cast<uint32_t>(quad * 32) << 16);
       bool write_c = true;
       const float4* other = nullptr;
-      if (it.tail >= 0 && push.n == 0) {  // (pushed K halves simply both add into the owner's buffer)
+      if (it.tail >= 0 && MODE != kPush) {  // (pushed K halves simply both add into the owner's buffer)
         // leave this K half in the workspace, then see whether the other half is already there
         // scratch layout per (tail tile, K half, CTA): [64 groups of 4 columns][128 rows] float4, so that
         // the 32 lanes of a warp (32 consecutive rows) write and read consecutive 16-byte words
@@ -310,8 +314,10 @@ __global__ void __launch_bounds__(kThreads2, 1)
         epi_sync();  // everybody has read the ticket before the next item overwrites it
         if (write_c && warp == 2 && lane == 0) tickets[it.tail * 2 + rank] = 0;
       }
-      float row_acc = epi.reduce_kind == FRISK_B200_REDUCE_MAX ? -INFINITY
-                      : epi.reduce_kind == FRISK_B200_REDUCE_MIN ? INFINITY : 0.f;
+      float row_acc = 0.f;
+      if (MODE == kFused)
+        row_acc = epi.reduce_kind == FRISK_B200_REDUCE_MAX ? -INFINITY
+                  : epi.reduce_kind == FRISK_B200_REDUCE_MIN ? INFINITY : 0.f;
       if (write_c) {
 #pragma unroll 1
         for (int c = 0; c < BN2 / 32; ++c) {
@@ -329,7 +335,7 @@ __global__ void __launch_bounds__(kThreads2, 1)
             }
           }
           const int col = n0 + c * 32;
-          if (push.n > 0) {
+          if (MODE == kPush) {
             // split-K across GPUs: add this chunk into the buffer of the GPU that owns the row
             if (row < M && col < N) {
               const int owner = row / push.rows_per_target;
@@ -343,12 +349,12 @@ __global__ void __launch_bounds__(kThreads2, 1)
             }
           } else if (row < M && col < N) {
             const int valid = min(32, N - col);
-            if (epi.has_fill) {
+            if (MODE == kFused && epi.has_fill) {
 #pragma unroll
               for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) + epi.fill);
             }
             store_row_chunk<TO>(C + (int64_t)row * ldc + col, v, valid, vec_c != 0, accumulate != 0);
-            if (epi.reduce_kind) {
+            if (MODE == kFused && epi.reduce_kind) {
               // over the values as they were stored (accumulate is off whenever a reduction is fused)
 #pragma unroll
               for (int i = 0; i < 32; ++i) {
@@ -361,7 +367,7 @@ __global__ void __launch_bounds__(kThreads2, 1)
             }
           }
         }
-        if (epi.reduce_kind && row < M) epi.row_partials[(int64_t)tc.n * M + row] = row_acc;
+        if (MODE == kFused && epi.reduce_kind && row < M) epi.row_partials[(int64_t)tc.n * M + row] = row_acc;
       }
       tc_fence_before_sync();
       __syncwarp();
@@ -417,7 +423,7 @@ TailPlan make_tail_plan(const frisk_b200_gemm_desc& d, int pairs_available) {
   return t;
 }
 
-template <typename TO, bool BF16, bool A_MN, bool B_MN>
+template <typename TO, bool BF16, bool A_MN, bool B_MN, int MODE>
 int launch_cfg2(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc& d, const void* A, const void* B, void* C,
                 void* ws, size_t ws_bytes, cudaStream_t s, const PushTargets* push_in = nullptr,
                 const EpilogueArgs* epi_in = nullptr) {
@@ -435,7 +441,7 @@ int launch_cfg2(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc& d, const void* 
     rc = encode_tmap_2d(&tb, d.dtype_ab, B, (uint64_t)g.K, (uint64_t)g.N, (uint64_t)g.ldb * 2, BK, BNC, true);
   if (rc) { ctx->last_cuda = rc; return FRISK_B200_E_CUDA; }
 
-  auto kern = gemm_tcgen05_2cta_kernel<TO, BF16, A_MN, B_MN>;
+  auto kern = gemm_tcgen05_2cta_kernel<TO, BF16, A_MN, B_MN, MODE>;
   FB_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem2::kTotal));
   cudaLaunchConfig_t cfg = {};
   cudaLaunchAttribute attr[1];
@@ -458,14 +464,14 @@ int launch_cfg2(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc& d, const void* 
   if (push_in) push = *push_in;
   EpilogueArgs epi{};
   if (epi_in) epi = *epi_in;
-  if (tp.bytes && push.n == 0 && (!ws || ws_bytes < tp.bytes)) {
+  if (tp.bytes && MODE != kPush && (!ws || ws_bytes < tp.bytes)) {
     // no scratch: run every tile whole
     tp.n_full = tp.n_items = tp.n_full + tp.tail_tiles;
     tp.tail_tiles = 0;
   }
   cfg.gridDim = dim3(2 * tp.pairs);
   unsigned* tickets = static_cast<unsigned*>(ws);
-  float* partials = (tp.tail_tiles && push.n == 0) ? reinterpret_cast<float*>(static_cast<unsigned char*>(ws) + tp.off_partials) : nullptr;
+  float* partials = (tp.tail_tiles && MODE != kPush) ? reinterpret_cast<float*>(static_cast<unsigned char*>(ws) + tp.off_partials) : nullptr;
   int vec_c = aligned16(C) && (g.ldc * sizeof(TO)) % 16 == 0;
   TO* Cp = static_cast<TO*>(C);
   int Mi = (int)g.M, Ni = (int)g.N, Ki = (int)g.K, acc = (d.clear_accum || epi.has_fill) ? 0 : 1;
@@ -477,16 +483,16 @@ int launch_cfg2(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc& d, const void* 
   return 0;
 }
 
-template <typename TO, bool BF16>
+template <typename TO, bool BF16, int MODE>
 int launch_major2(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc& d, const void* A, const void* B, void* C,
                   void* ws, size_t ws_bytes, cudaStream_t s, const EpilogueArgs* epi) {
   bool a_mn = d.trans_a != 0, b_mn = d.trans_b == 0;
   if (a_mn) {
-    if (b_mn) return launch_cfg2<TO, BF16, true, true>(ctx, d, A, B, C, ws, ws_bytes, s, nullptr, epi);
-    return launch_cfg2<TO, BF16, true, false>(ctx, d, A, B, C, ws, ws_bytes, s, nullptr, epi);
+    if (b_mn) return launch_cfg2<TO, BF16, true, true, MODE>(ctx, d, A, B, C, ws, ws_bytes, s, nullptr, epi);
+    return launch_cfg2<TO, BF16, true, false, MODE>(ctx, d, A, B, C, ws, ws_bytes, s, nullptr, epi);
   }
-  if (b_mn) return launch_cfg2<TO, BF16, false, true>(ctx, d, A, B, C, ws, ws_bytes, s, nullptr, epi);
-  return launch_cfg2<TO, BF16, false, false>(ctx, d, A, B, C, ws, ws_bytes, s, nullptr, epi);
+  if (b_mn) return launch_cfg2<TO, BF16, false, true, MODE>(ctx, d, A, B, C, ws, ws_bytes, s, nullptr, epi);
+  return launch_cfg2<TO, BF16, false, false, MODE>(ctx, d, A, B, C, ws, ws_bytes, s, nullptr, epi);
 }
 
 }  // namespace
@@ -506,8 +512,8 @@ int launch_gemm_tcgen05_2cta_push(frisk_b200_ctx* ctx, const frisk_b200_gemm_des
   const bool a_mn = d.trans_a != 0, b_mn = d.trans_b == 0;
   if (a_mn || b_mn) return FRISK_B200_E_UNSUPPORTED;  // the K-split path keeps both operands K-contiguous
   if (d.dtype_ab == FRISK_B200_BF16)
-    return launch_cfg2<float, true, false, false>(ctx, d, A, B, nullptr, nullptr, 0, s, &push);
-  return launch_cfg2<float, false, false, false>(ctx, d, A, B, nullptr, nullptr, 0, s, &push);
+    return launch_cfg2<float, true, false, false, kPush>(ctx, d, A, B, nullptr, nullptr, 0, s, &push);
+  return launch_cfg2<float, false, false, false, kPush>(ctx, d, A, B, nullptr, nullptr, 0, s, &push);
 }
 
 int tcgen05_2cta_column_tiles(const frisk_b200_gemm_desc& d) { return (int)((resolve_dims(d).N + BN2 - 1) / BN2); }
@@ -525,11 +531,18 @@ int launch_gemm_tcgen05_2cta(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc& d,
   if (!tcgen05_supported(d)) return FRISK_B200_E_UNSUPPORTED;
   if (!aligned16(A) || !aligned16(B)) return FRISK_B200_E_ALIGN;
   const bool bf = d.dtype_ab == FRISK_B200_BF16;
+  if (epi && (epi->has_fill || epi->reduce_kind)) {
+    if (d.dtype_c == FRISK_B200_F32)
+      return bf ? launch_major2<float, true, kFused>(ctx, d, A, B, C, ws, ws_bytes, s, epi)
+                : launch_major2<float, false, kFused>(ctx, d, A, B, C, ws, ws_bytes, s, epi);
+    if (bf) return launch_major2<__nv_bfloat16, true, kFused>(ctx, d, A, B, C, ws, ws_bytes, s, epi);
+    return launch_major2<__half, false, kFused>(ctx, d, A, B, C, ws, ws_bytes, s, epi);
+  }
   if (d.dtype_c == FRISK_B200_F32)
-    return bf ? launch_major2<float, true>(ctx, d, A, B, C, ws, ws_bytes, s, epi)
-              : launch_major2<float, false>(ctx, d, A, B, C, ws, ws_bytes, s, epi);
-  if (bf) return launch_major2<__nv_bfloat16, true>(ctx, d, A, B, C, ws, ws_bytes, s, epi);
-  return launch_major2<__half, false>(ctx, d, A, B, C, ws, ws_bytes, s, epi);
+    return bf ? launch_major2<float, true, kStore>(ctx, d, A, B, C, ws, ws_bytes, s, nullptr)
+              : launch_major2<float, false, kStore>(ctx, d, A, B, C, ws, ws_bytes, s, nullptr);
+  if (bf) return launch_major2<__nv_bfloat16, true, kStore>(ctx, d, A, B, C, ws, ws_bytes, s, nullptr);
+  return launch_major2<__half, false, kStore>(ctx, d, A, B, C, ws, ws_bytes, s, nullptr);
 }
 
 }  // namespace fb
