@@ -8,6 +8,9 @@ attention path (``python/frisk/__init__.py:1-4``): the builder classes of
 from . import capi, ir
 from .execute import attention_forward, attention_geometry, execute, fused_plan, gemm, gemm_plan
 from .helper import FriskHelper, create_context, create_session
+from .affine import (AffineBinaryOpExpr, AffineConstantExpr, AffineDimExpr, AffineExpr, AffineExprKind,
+                     AffineSymbolExpr, get_affine_binary_op_expr, get_affine_constant_expr, get_affine_constant_exprs,
+                     get_affine_dim_expr, get_affine_symbol_expr)
 from .ir import (AffineMap, AllocBufferOp, BlockOp, CopyOp, FillOp, ForOp, GemmOp, GemmWarpPolicy, KernelOp,
                  MemorySpace, OpState, ParallelOp, ReduceOp, block, builder, context, frisk, module, type, value)
 

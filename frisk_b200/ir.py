@@ -125,26 +125,9 @@ def _float_from_string(dtype):
     return type("float", name=_FLOAT_STRINGS[dtype])
 
 
-class AffineMap:
-    """Default-constructed (null), identity or empty map."""
-
-    def __init__(self, rank=None, empty=False):
-        self.rank, self.empty = rank, empty
-
-    def __bool__(self):
-        return self.rank is not None or self.empty
-
-    def is_identity(self):
-        return not self.empty
-
-    def get_num_inputs(self):
-        return 0 if (self.empty or self.rank is None) else self.rank
-
-    def __str__(self):
-        if self.empty:
-            return "affine_map<() -> ()>"
-        dims = ", ".join(f"d{i}" for i in range(self.rank or 0))
-        return f"affine_map<({dims}) -> ({dims})>"
+from .affine import (AffineExpr, AffineExprKind, AffineMap, get_affine_binary_op_expr,  # noqa: E402,F401
+                     get_affine_constant_expr, get_affine_constant_exprs, get_affine_dim_expr,
+                     get_affine_symbol_expr)
 
 
 # ------------------------------------------------------------------------ IR skeleton
@@ -576,6 +559,16 @@ class builder:  # noqa: N801
 
     def get_float_attr(self, v, dtype):
         return (float(v), _float_from_string(dtype))
+
+    # affine expressions (ffi/ir.cpp:303-308)
+    def get_affine_dim_expr(self, position):
+        return get_affine_dim_expr(position)
+
+    def get_affine_symbol_expr(self, position):
+        return get_affine_symbol_expr(position)
+
+    def get_affine_constant_expr(self, value):
+        return get_affine_constant_expr(value)
 
     def get_empty_affine_map(self):
         return AffineMap(empty=True)

@@ -207,7 +207,7 @@ def test_fused_plan_folds_fill_and_reduce_into_the_gemm():
 REFERENCE_TESTS = "/root/reference/test/python"
 
 
-@pytest.mark.parametrize("script", ["bind_test.py", "helper_test.py", "test.py"])
+@pytest.mark.parametrize("script", ["bind_test.py", "helper_test.py", "map_expr_test.py", "test.py"])
 def test_reference_builder_scripts_run_verbatim(script, capsys):
     """The reference's own builder scripts (`import frisk as F`), unmodified, against this
     package under the name `frisk`.  Skipped where the reference checkout is not present."""
@@ -229,3 +229,35 @@ def test_reference_builder_scripts_run_verbatim(script, capsys):
     out = capsys.readouterr().out
     if script == "bind_test.py":
         assert "frisk.gemm" in out and "frisk.reduce" in out and "frisk.fill" in out
+    if script == "map_expr_test.py":
+        assert out.splitlines()[0] == "d0 * 5 + s0" and "(d0)[s0] -> ((d0 * 5 + s0) * 2)" in out
+
+
+def test_affine_expressions_simplify_and_print_like_the_reference_binding():
+    """ffi/ir.cpp:640-875 binds MLIR's AffineExpr / AffineMap; these are the documented construction-time
+    simplifications and printer forms of those classes."""
+    b = F.builder(F.context())
+    d0, d1, s0 = b.get_affine_dim_expr(0), b.get_affine_dim_expr(1), b.get_affine_symbol_expr(0)
+    c = b.get_affine_constant_expr
+    assert str(d0 * c(5) + s0 + c(0)) == "d0 * 5 + s0"
+    assert str(3 + d0 + 4) == "d0 + 7" and str((d0 * 2) * 3) == "d0 * 6"
+    assert str(d0 - d1) == "d0 - d1" and str(d0 * 2 - s0 * 3) == "d0 * 2 - s0 * 3" and str(d0 - 3) == "d0 - 3"
+    assert str((d0 + 1) * 2) == "(d0 + 1) * 2" and str(-(d0 + 1)) == "-(d0 + 1)"
+    assert str((d0 + d1).floor_div(4)) == "(d0 + d1) floordiv 4" and (d0 * 8) % 4 == 0
+    assert str((d0 * 8).floor_div(4)) == "d0 * 2" and str(d0.ceil_div(1)) == "d0"
+    assert str(s0 * d0) == "d0 * s0" and str(d0 + d0) == "d0 * 2" and (d0 - d0) == 0
+    assert c(7).floor_div(2) == 3 and c(-7).floor_div(2) == -4 and c(7).ceil_div(2) == 4 and c(-7) % 4 == 1
+    with pytest.raises(ValueError):
+        d0 * d1
+    e = d0 * 5 + s0
+    assert e.get_kind() == F.AffineExprKind.Add and str(e.get_kind()) == "AffineExprKind.Add"
+    assert str(e.as_binary().get_lhs()) == "d0 * 5" and e.as_dim() is None and d1.as_dim().get_position() == 1
+    assert e.is_pure_affine() and not e.is_symbolic_or_constant() and e.is_function_of_dim(0) and not e.is_function_of_dim(1)
+    assert str(e.replace_dims_and_symbols([d1 + 1], [c(2)])) == "(d1 + 1) * 5 + 2"  # no flattening on construction
+    m = F.AffineMap.get(2, 1, [d0 + s0, d1], None)
+    assert str(m) == "(d0, d1)[s0] -> (d0 + s0, d1)" and m.get_num_inputs() == 3 and not m.is_identity()
+    assert F.AffineMap.get_multi_dim_identity_map(2, None).is_identity()
+    assert str(F.AffineMap.get_permutation_map([1, 0], None)) == "(d0, d1) -> (d1, d0)"
+    assert F.AffineMap.get_permutation_map([1, 0], None).is_permutation()
+    assert not F.AffineMap() and str(F.AffineMap()) == "<<NULL AFFINE MAP>>" and F.AffineMap.get(None).is_empty()
+    assert F.AffineMap.get_constant_map(5, None).get_single_constant_result() == 5
