@@ -290,7 +290,7 @@ def run_ours(args):
 
 def splitk_secondary(ctx, torch, dist, world, rank, peaks):
     """bf16 GEMM M=N=8192, K=131072 with K split across the ranks, two ways: (fused) the tcgen05
-    epilogue adds each fp32 tile into the row owner's memory over NVLink; (nccl) fp32 partials,
+    epilogue stores each fp32 tile into its slot in the row owner's memory over NVLink; (nccl) fp32 partials,
     NCCL reduce-scatter pipelined over row panels, local rounding to bf16."""
     from frisk_b200 import splitk
     M, N, K = 8192, 8192, 131072
@@ -312,7 +312,7 @@ def splitk_secondary(ctx, torch, dist, world, rank, peaks):
         op = splitk.SplitKGemmPush(M, N, K, world, rank, "bf16", ctx, dist.group.WORLD)
         total, per, _ = time_steps(lambda i: op.run(a, b), 5, 3, torch, dist, world)
         ctx.check(torch.cuda.current_stream().cuda_stream)
-        res["fused_push"] = line(total / 5, "epilogue red.global.add.v4.f32 into peer memory, %.1f MB sent per GPU" % sent)
+        res["fused_push"] = line(total / 5, "epilogue 16-byte stores into this rank's slot in the owners' memory, slots summed in rank order, %.1f MB sent per GPU" % sent)
         dist.barrier()
         op.close()
     except Exception as e:  # noqa: BLE001

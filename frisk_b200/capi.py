@@ -25,7 +25,7 @@ EXPORTS = (
     "frisk_b200_gemm_select", "frisk_b200_gemm_workspace_bytes", "frisk_b200_gemm", "frisk_b200_gemm_host",
     "frisk_b200_attention_validate", "frisk_b200_attention_workspace_bytes", "frisk_b200_attention_fwd",
     "frisk_b200_attention_fwd_host", "frisk_b200_convert_f32", "frisk_b200_check",
-    "frisk_b200_gemm_skinny_static", "frisk_b200_gemm_push", "frisk_b200_convert_f32_clear",
+    "frisk_b200_gemm_skinny_static", "frisk_b200_gemm_push", "frisk_b200_sum_slots",
     "frisk_b200_peer_buffer_create", "frisk_b200_peer_buffer_open", "frisk_b200_peer_buffer_close",
     "frisk_b200_gemm_fused_select", "frisk_b200_gemm_fused_workspace_bytes", "frisk_b200_gemm_fused",
 )
@@ -106,7 +106,7 @@ def load():
         "frisk_b200_check": (ctypes.c_int, [vp, vp]),
         "frisk_b200_gemm_skinny_static": (ctypes.c_int, [ctypes.c_int, gd, vp, vp, vp, vp]),
         "frisk_b200_gemm_push": (ctypes.c_int, [vp, gd, vp, vp, ctypes.POINTER(vp), i32, i64, i64, vp]),
-        "frisk_b200_convert_f32_clear": (ctypes.c_int, [vp, vp, vp, i64, i32, vp]),
+        "frisk_b200_sum_slots": (ctypes.c_int, [vp, vp, i32, i64, vp, i64, i32, vp]),
         "frisk_b200_peer_buffer_create": (ctypes.c_int, [vp, sz, ctypes.POINTER(vp), vp]),
         "frisk_b200_peer_buffer_open": (ctypes.c_int, [vp, vp, ctypes.POINTER(vp)]),
         "frisk_b200_peer_buffer_close": (ctypes.c_int, [vp, vp, i32]),
@@ -209,9 +209,10 @@ class Context:
                                          rows_per_target, ld_target, stream)
         raise_for(rc, self._h)
 
-    def convert_f32_clear(self, src_ptr, dst_ptr, count, dtype, stream=None):
+    def sum_slots(self, slots_ptr, n_slots, slot_elems, dst_ptr, count, dtype, stream=None):
         code = DTYPE_CODE[dtype] if isinstance(dtype, str) else dtype
-        raise_for(load().frisk_b200_convert_f32_clear(self.handle, src_ptr, dst_ptr, count, code, stream), self._h)
+        raise_for(load().frisk_b200_sum_slots(self.handle, slots_ptr, n_slots, slot_elems, dst_ptr, count, code,
+                                              stream), self._h)
 
     def peer_buffer_create(self, nbytes):
         """-> (device pointer, 64-byte handle) of a zeroed buffer other processes can map."""

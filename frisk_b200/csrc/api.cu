@@ -87,39 +87,47 @@ __global__ void convert_f32_kernel(const float* __restrict__ src, T* __restrict_
 }  // namespace
 
 namespace {
-// round and clear in one pass: the accumulation buffer is ready for the next product
+// dst[i] = round(slots[0][i] + slots[1][i] + ...), in slot order: the partial products the ranks of a
+// K-split GEMM stored into this GPU's slots, summed and rounded in one pass over them
 template <typename T>
-__global__ void convert_f32_clear_kernel(float* __restrict__ src, T* __restrict__ dst, int64_t n) {
+__global__ void sum_slots_kernel(const float* __restrict__ slots, int n_slots, int64_t slot_elems,
+                                 T* __restrict__ dst, int64_t n) {
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   const int64_t n8 = n / 8;
-  const bool vec = (reinterpret_cast<uintptr_t>(src) & 15u) == 0 && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0;
+  const bool vec = (reinterpret_cast<uintptr_t>(slots) & 15u) == 0 && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0 &&
+                   slot_elems % 4 == 0;
   if (vec) {
     for (int64_t v = i; v < n8; v += stride) {
-      float4 a = reinterpret_cast<const float4*>(src)[2 * v];
-      float4 b = reinterpret_cast<const float4*>(src)[2 * v + 1];
+      float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
+      for (int s = 0; s < n_slots; ++s) {
+        const float4* p = reinterpret_cast<const float4*>(slots + (int64_t)s * slot_elems);
+        const float4 x = __ldcs(p + 2 * v), y = __ldcs(p + 2 * v + 1);
+        a.x += x.x; a.y += x.y; a.z += x.z; a.w += x.w;
+        b.x += y.x; b.y += y.y; b.z += y.z; b.w += y.w;
+      }
       T o[8] = {T(a.x), T(a.y), T(a.z), T(a.w), T(b.x), T(b.y), T(b.z), T(b.w)};
       reinterpret_cast<uint4*>(dst)[v] = *reinterpret_cast<uint4*>(o);
-      reinterpret_cast<float4*>(src)[2 * v] = make_float4(0.f, 0.f, 0.f, 0.f);
-      reinterpret_cast<float4*>(src)[2 * v + 1] = make_float4(0.f, 0.f, 0.f, 0.f);
     }
   }
   for (int64_t k = (vec ? n8 * 8 : 0) + i; k < n; k += stride) {
-    dst[k] = T(src[k]);
-    src[k] = 0.f;
+    float acc = 0.f;
+    for (int s = 0; s < n_slots; ++s) acc += slots[(int64_t)s * slot_elems + k];
+    dst[k] = T(acc);
   }
 }
 }  // namespace
 
-int launch_convert_f32_clear(float* src, void* dst, int64_t n, int dtype, cudaStream_t s) {
+int launch_sum_slots(const float* slots, int n_slots, int64_t slot_elems, void* dst, int64_t n, int dtype,
+                     cudaStream_t s) {
   if (n <= 0) return 0;
   int blocks = (int)((n / 8 + 255) / 256);
   if (blocks < 1) blocks = 1;
   if (blocks > 148 * 16) blocks = 148 * 16;
   if (dtype == FRISK_B200_F16)
-    convert_f32_clear_kernel<__half><<<blocks, 256, 0, s>>>(src, static_cast<__half*>(dst), n);
+    sum_slots_kernel<__half><<<blocks, 256, 0, s>>>(slots, n_slots, slot_elems, static_cast<__half*>(dst), n);
   else if (dtype == FRISK_B200_BF16)
-    convert_f32_clear_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>(src, static_cast<__nv_bfloat16*>(dst), n);
+    sum_slots_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>(slots, n_slots, slot_elems, static_cast<__nv_bfloat16*>(dst), n);
   else
     return FRISK_B200_E_UNSUPPORTED;
   return cudaGetLastError() == cudaSuccess ? 0 : FRISK_B200_E_CUDA;
@@ -437,7 +445,8 @@ int frisk_b200_gemm_host(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc* d, con
   // copy-out of panel p overlaps the copy-in of panel p+1).  Only when A's rows are
   // contiguous in the buffer (trans_a = 0) and the problem is large enough to split.
   int panels = 1;
-  if (!d->trans_a && algo != FRISK_B200_ALGO_SKINNY && g.M >= 1024 && e.a + e.c >= ((size_t)8 << 20)) panels = 4;
+  if (!d->trans_a && algo != FRISK_B200_ALGO_SKINNY && g.M >= 1024 && e.a + e.c >= ((size_t)8 << 20))
+    panels = (g.M >= 4096 && e.a + e.c >= ((size_t)48 << 20)) ? 8 : 4;  // the last panel's copy-out is the exposed tail
   const int64_t rows_per = ((g.M + panels - 1) / panels + 255) / 256 * 256;
   panels = (int)((g.M + rows_per - 1) / rows_per);
 
@@ -681,11 +690,11 @@ int frisk_b200_gemm_fused(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc* d, co
   return rc;
 }
 
-int frisk_b200_convert_f32_clear(frisk_b200_ctx* ctx, float* src, void* dst, int64_t count, int32_t dtype_dst,
-                                 void* stream) {
-  if (!ctx || !src || !dst || count < 0) return FRISK_B200_E_ARG;
+int frisk_b200_sum_slots(frisk_b200_ctx* ctx, const float* slots, int32_t n_slots, int64_t slot_elems, void* dst,
+                         int64_t count, int32_t dtype_dst, void* stream) {
+  if (!ctx || !slots || !dst || count < 0 || n_slots < 1 || slot_elems < count) return FRISK_B200_E_ARG;
   FB_CUDA(ctx, cudaSetDevice(ctx->device));
-  return launch_convert_f32_clear(src, dst, count, dtype_dst, static_cast<cudaStream_t>(stream));
+  return launch_sum_slots(slots, n_slots, slot_elems, dst, count, dtype_dst, static_cast<cudaStream_t>(stream));
 }
 
 // ---- buffers other processes on this node can map (cudaIpc): the destinations of frisk_b200_gemm_push

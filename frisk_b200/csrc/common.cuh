@@ -87,9 +87,9 @@ bool tcgen05_supported(const frisk_b200_gemm_desc& d);
 int launch_gemm_tcgen05(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc& d, const void* A, const void* B,
                         void* C, cudaStream_t s);
 
-// Row blocks of the fp32 product are added into up to 8 destination buffers instead of being
-// stored: destination i receives rows [i*rows_per_target, (i+1)*rows_per_target) (it may be a
-// peer GPU's memory, reached with plain reductions over NVLink; never with TMA).
+// Row blocks of the fp32 product are stored into up to 8 destination buffers instead of C:
+// destination i receives rows [i*rows_per_target, (i+1)*rows_per_target) (it may be a peer
+// GPU's memory, reached with plain stores over NVLink; never with TMA).
 struct PushTargets {
   float* ptr[8];
   int n;                 // 0 = ordinary store to C
@@ -107,7 +107,8 @@ struct EpilogueArgs {
 bool tcgen05_2cta_preferred(const frisk_b200_gemm_desc& d);
 int launch_gemm_tcgen05_2cta_push(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc& d, const void* A, const void* B,
                                   const PushTargets& push, cudaStream_t s);
-int launch_convert_f32_clear(float* src, void* dst, int64_t n, int dtype, cudaStream_t s);
+int launch_sum_slots(const float* slots, int n_slots, int64_t slot_elems, void* dst, int64_t n, int dtype,
+                     cudaStream_t s);
 // scratch for the K-split tail wave (0 when every tile runs whole); tickets at its start must be zero
 size_t tcgen05_2cta_workspace_bytes(const frisk_b200_gemm_desc& d);
 int launch_gemm_tcgen05_2cta(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc& d, const void* A, const void* B,

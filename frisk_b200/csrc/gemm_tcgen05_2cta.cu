@@ -94,12 +94,6 @@ __device__ __forceinline__ void umma_f16_ss_pair(uint32_t tmem_d, uint64_t desc_
       ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
       : "memory");
 }
-// 16-byte fp32 reduction into global memory (local or a peer's): no return value, fire and forget
-__device__ __forceinline__ void red_add_v4(float* dst, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
-  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(__uint_as_float(a)),
-               "f"(__uint_as_float(b)), "f"(__uint_as_float(c)), "f"(__uint_as_float(d))
-               : "memory");
-}
 // arrive on the barrier at the same shared-memory offset in every CTA of `mask` once all MMAs
 // issued so far have completed
 __device__ __forceinline__ void umma_commit_pair(uint64_t* bar, uint16_t mask) {
@@ -288,7 +282,7 @@ __global__ void __launch_bounds__(kThreads2, 1)
       const uint32_t taddr = tmem_base + acc * BN2 + (static_cast<uint32_t>(quad * 32) << 16);
       bool write_c = true;
       const float4* other = nullptr;
-      if (it.tail >= 0 && MODE != kPush) {  // (pushed K halves simply both add into the owner's buffer)
+      if (it.tail >= 0) {  // (pushed K halves simply both add into the owner's buffer)
         // leave this K half in the workspace, then see whether the other half is already there
         // scratch layout per (tail tile, K half, CTA): [64 groups of 4 columns][128 rows] float4, so that
         // the 32 lanes of a warp (32 consecutive rows) write and read consecutive 16-byte words
@@ -336,15 +330,19 @@ __global__ void __launch_bounds__(kThreads2, 1)
           }
           const int col = n0 + c * 32;
           if (MODE == kPush) {
-            // split-K across GPUs: add this chunk into the buffer of the GPU that owns the row
+            // split-K across GPUs: store this chunk into this rank's slot at the GPU that owns the row
+            // (plain 16-byte stores; over NVLink they pipeline like a peer copy, remote atomics do not)
             if (row < M && col < N) {
               const int owner = row / push.rows_per_target;
               float* dst = push.ptr[owner] + (int64_t)(row - owner * push.rows_per_target) * push.ld + col;
               if (col + 32 <= N && (push.ld & 3) == 0) {
 #pragma unroll
-                for (int i = 0; i < 8; ++i) red_add_v4(dst + 4 * i, v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+                for (int i = 0; i < 8; ++i)
+                  *reinterpret_cast<float4*>(dst + 4 * i) =
+                      make_float4(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]), __uint_as_float(v[4 * i + 2]),
+                                  __uint_as_float(v[4 * i + 3]));
               } else {
-                for (int i = 0; i < 32 && col + i < N; ++i) atomicAdd(dst + i, __uint_as_float(v[i]));
+                for (int i = 0; i < 32 && col + i < N; ++i) dst[i] = __uint_as_float(v[i]);
               }
             }
           } else if (row < M && col < N) {
@@ -464,14 +462,14 @@ int launch_cfg2(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc& d, const void* 
   if (push_in) push = *push_in;
   EpilogueArgs epi{};
   if (epi_in) epi = *epi_in;
-  if (tp.bytes && MODE != kPush && (!ws || ws_bytes < tp.bytes)) {
+  if (tp.bytes && (MODE == kPush || !ws || ws_bytes < tp.bytes)) {
     // no scratch: run every tile whole
     tp.n_full = tp.n_items = tp.n_full + tp.tail_tiles;
     tp.tail_tiles = 0;
   }
   cfg.gridDim = dim3(2 * tp.pairs);
   unsigned* tickets = static_cast<unsigned*>(ws);
-  float* partials = (tp.tail_tiles && MODE != kPush) ? reinterpret_cast<float*>(static_cast<unsigned char*>(ws) + tp.off_partials) : nullptr;
+  float* partials = tp.tail_tiles ? reinterpret_cast<float*>(static_cast<unsigned char*>(ws) + tp.off_partials) : nullptr;
   int vec_c = aligned16(C) && (g.ldc * sizeof(TO)) % 16 == 0;
   TO* Cp = static_cast<TO*>(C);
   int Mi = (int)g.M, Ni = (int)g.N, Ki = (int)g.K, acc = (d.clear_accum || epi.has_fill) ? 0 : 1;
@@ -504,7 +502,7 @@ bool tcgen05_2cta_preferred(const frisk_b200_gemm_desc& d) {
   return tiles >= kNumSMsDefault / 2;
 }
 
-// Split-K across GPUs: the same kernel, its epilogue adding every fp32 tile into the row owner's buffer.
+// Split-K across GPUs: the same kernel, its epilogue storing every fp32 tile into this rank's slot at the row's owner.
 int launch_gemm_tcgen05_2cta_push(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc& d, const void* A, const void* B,
                                   const PushTargets& push, cudaStream_t s) {
   if (!tcgen05_supported(d) || d.dtype_c != FRISK_B200_F32) return FRISK_B200_E_UNSUPPORTED;

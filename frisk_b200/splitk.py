@@ -148,16 +148,17 @@ class SplitKGemm:
 
 class SplitKGemmPush:
     """The same K-split product with the exchange FUSED into the GEMM: the epilogue of the
-    tcgen05 kernel adds every finished fp32 tile straight into the memory of the GPU that owns
-    its rows (``frisk_b200_gemm_push``: 16-byte ``red.global.add`` over NVLink to buffers mapped
-    with cudaIpc), so the transfer overlaps the arithmetic tile by tile and no SM is taken away
-    by a collective kernel.  Rank r owns rows ``[r*M/g, (r+1)*M/g)``.
+    tcgen05 kernel stores every finished fp32 tile straight into the memory of the GPU that owns
+    its rows (``frisk_b200_gemm_push``: 16-byte stores over NVLink to buffers mapped with
+    cudaIpc), so the transfer overlaps the arithmetic tile by tile and no SM is taken away by a
+    collective kernel.  Rank r owns rows ``[r*M/g, (r+1)*M/g)`` and holds one slot of that many
+    rows per rank; rank s writes only slot s, everywhere.
 
-    Per call: push; a one-element all-reduce on the stream as the cross-GPU barrier (every
-    rank's pushes are then complete); round this rank's rows to 16 bits and clear them.  Two
-    accumulation buffers alternate, so a rank that is already pushing call i+1 can never reach a
-    buffer its peer has not yet cleared after call i-1.  The additions arrive in no fixed
-    order: results are reproducible to fp32 rounding, not bit for bit."""
+    Per call: push; a one-element all-reduce on the stream as the cross-GPU barrier (every rank's
+    stores are then complete); sum this rank's g slots in slot order and round them
+    (``frisk_b200_sum_slots``) -- the result does not depend on timing.  Two sets of slots
+    alternate, so a rank that is already pushing call i+1 can never overwrite a slot its peer has
+    not yet summed for call i."""
 
     def __init__(self, M, N, K, world, rank, dtype, ctx, group=None):
         import torch
@@ -166,18 +167,21 @@ class SplitKGemmPush:
             raise ValueError("split-k push: M and K must divide by the number of ranks (<= 8)")
         self.M, self.N, self.k_local, self.world, self.rank = M, N, K // world, world, rank
         self.rows = M // world
+        self.slot_elems = self.rows * N
         self.ctx, self.group, self.dtype = ctx, group, dtype
         self.device = torch.device("cuda", torch.cuda.current_device())
-        self.own, self.targets = [], []
+        self.own, self.mapped, self.targets = [], [], []
         for _ in range(2):
-            ptr, handle = ctx.peer_buffer_create(self.rows * N * 4)
+            ptr, handle = ctx.peer_buffer_create(world * self.slot_elems * 4)
             handles = [None] * world
             if world > 1:
                 dist.all_gather_object(handles, handle, group=group)
             else:
                 handles = [handle]
+            bases = [ptr if r == rank else ctx.peer_buffer_open(handles[r]) for r in range(world)]
             self.own.append(ptr)
-            self.targets.append([ptr if r == rank else ctx.peer_buffer_open(handles[r]) for r in range(world)])
+            self.mapped.append(bases)
+            self.targets.append([b + rank * self.slot_elems * 4 for b in bases])  # this rank's slot at every owner
         self.out = torch.empty(self.rows, N, dtype={"bf16": torch.bfloat16, "fp16": torch.float16}[dtype],
                                device=self.device)
         self.token = torch.zeros(1, device=self.device)
@@ -198,11 +202,12 @@ class SplitKGemmPush:
                            stream=stream)
         if self.world > 1:
             dist.all_reduce(self.token, group=self.group)  # stream-ordered barrier across the GPUs
-        self.ctx.convert_f32_clear(self.own[buf], self.out.data_ptr(), self.rows * self.N, self.dtype, stream=stream)
+        self.ctx.sum_slots(self.own[buf], self.world, self.slot_elems, self.out.data_ptr(), self.slot_elems, self.dtype,
+                           stream=stream)
         return self.out
 
     def close(self):
-        for buf in range(2):
-            for r, ptr in enumerate(self.targets[buf]):
+        for buf in range(len(self.mapped)):
+            for r, ptr in enumerate(self.mapped[buf]):
                 self.ctx.peer_buffer_close(ptr, owned=(r == self.rank))
-        self.targets = []
+        self.mapped, self.targets = [], []

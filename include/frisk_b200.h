@@ -185,16 +185,17 @@ int frisk_b200_attention_fwd_host(frisk_b200_ctx* ctx, const frisk_b200_attn_des
 int frisk_b200_convert_f32(frisk_b200_ctx* ctx, const float* src, void* dst, int64_t count,
                            int32_t dtype_dst, void* stream);
 
-/* ---- fused split-K: GEMM whose fp32 result is ADDED into row-block owners -------------------
+/* ---- fused split-K: GEMM whose fp32 result is STORED at the row-block owners ----------------
  * No reference counterpart (the reference is single-GPU).  The fp32 product of this rank's K
- * slice is not stored: rows [i*rows_per_target, (i+1)*rows_per_target) are added, with 16-byte
- * red.global reductions issued from the GEMM epilogue, into targets[i] (row pitch ld_target
- * elements).  A target may be another GPU's memory mapped into this process
+ * slice is not written to a local C: rows [i*rows_per_target, (i+1)*rows_per_target) are
+ * stored, with 16-byte stores issued from the GEMM epilogue, into targets[i] (row pitch
+ * ld_target elements).  A target may be another GPU's memory mapped into this process
  * (frisk_b200_peer_buffer_open): the exchange then travels over NVLink tile by tile while the
- * tensor cores work on the next tile.  Requirements: dtype_c = F32, trans_a = 0, trans_b = 1,
- * n_targets <= 8; targets hold zero or an earlier sum.  The sums are complete once every
- * rank's kernel has finished (the caller places a cross-GPU barrier on the stream); the order
- * of the additions, hence the last bits, is not fixed. */
+ * tensor cores work on the next tile.  Each rank points its targets at ITS OWN slot of the
+ * owners' buffers; once every rank's kernel has finished (the caller places a cross-GPU
+ * barrier on the stream) an owner sums its slots in slot order with frisk_b200_sum_slots, so
+ * the result does not depend on timing.  Requirements: dtype_c = F32, trans_a = 0,
+ * trans_b = 1, n_targets <= 8. */
 int frisk_b200_gemm_push(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc* desc, const void* A,
                          const void* B, float* const* targets, int32_t n_targets,
                          int64_t rows_per_target, int64_t ld_target, void* stream);
@@ -235,9 +236,10 @@ int frisk_b200_gemm_fused(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc* desc,
                           const frisk_b200_gemm_epilogue* epi, const void* A, const void* B, void* C,
                           void* workspace, size_t workspace_bytes, void* stream);
 
-/* Round an fp32 buffer to 16 bits and zero it in the same pass (ready for the next push). */
-int frisk_b200_convert_f32_clear(frisk_b200_ctx* ctx, float* src, void* dst, int64_t count,
-                                 int32_t dtype_dst, void* stream);
+/* dst[i] = round(sum over s < n_slots of slots[s * slot_elems + i]), i < count, added in slot
+ * order in fp32 and rounded once to the 16-bit type. */
+int frisk_b200_sum_slots(frisk_b200_ctx* ctx, const float* slots, int32_t n_slots, int64_t slot_elems,
+                         void* dst, int64_t count, int32_t dtype_dst, void* stream);
 /* Device buffers that other processes of this node can map (cudaIpc): `handle64` is 64 bytes
  * to hand to the peers, which call _open.  _close frees (owned = 1) or unmaps (owned = 0). */
 int frisk_b200_peer_buffer_create(frisk_b200_ctx* ctx, size_t bytes, void** ptr, void* handle64);

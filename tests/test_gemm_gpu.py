@@ -252,38 +252,41 @@ def test_execute_bind_test_style(ctx):
 
 
 def test_gemm_push_into_row_block_owners(ctx):
-    """The fused split-K epilogue on one GPU: the fp32 product is added into two row-block
-    buffers (stand-ins for two GPUs' memories), twice, then rounded and cleared."""
+    """The fused split-K epilogue on one GPU: two "ranks" (K halves) store their fp32 products into
+    their slots of two row-block owners (stand-ins for two GPUs' memories), then each owner sums
+    its slots and rounds."""
     import torch
-    M, N, K = 1024, 768, 512
+    M, N, K = 1024, 768, 1024
     a, b = inputs.gemm_inputs(M, N, K, "bf16", False, True, 61, "normal_rsqrt_k")
-    da, db = to_device(a, "bf16"), to_device(b, "bf16")
-    t0 = torch.zeros(M // 2, N, device="cuda")
-    t1 = torch.zeros(M // 2, N, device="cuda")
-    desc = capi.gemm_desc(M, N, K, "bf16", "fp32", False, True, clear_accum=True, algo=capi.ALGO_TCGEN05_PAIR)
+    rows = M // 2
+    owners = [torch.full((2, rows, N), float("nan"), device="cuda") for _ in range(2)]  # [slot][rows][N] per owner
+    desc = capi.gemm_desc(M, N, K // 2, "bf16", "fp32", False, True, clear_accum=True, algo=capi.ALGO_TCGEN05_PAIR)
     s = torch.cuda.current_stream().cuda_stream
-    for _ in range(2):  # two ranks' worth of the same partial product
-        ctx.gemm_push(desc, da.data_ptr(), db.data_ptr(), [t0.data_ptr(), t1.data_ptr()], M // 2, N, stream=s)
+    for rank in range(2):
+        da = to_device(np.ascontiguousarray(a[:, rank * (K // 2):(rank + 1) * (K // 2)]), "bf16")
+        db = to_device(np.ascontiguousarray(b[:, rank * (K // 2):(rank + 1) * (K // 2)]), "bf16")
+        ctx.gemm_push(desc, da.data_ptr(), db.data_ptr(), [o[rank].data_ptr() for o in owners], rows, N, stream=s)
     ctx.check(s)
-    ref = 2.0 * gemm_oracle.gemm_fp64(a, b, "bf16", False, True)
-    got = torch.cat([t0, t1]).cpu().numpy()
+    ref = gemm_oracle.gemm_fp64(a, b, "bf16", False, True)
+    got = torch.cat([o.sum(dim=0) for o in owners]).cpu().numpy()
     assert rel_frobenius(got, ref) <= 1e-5
-    out = torch.empty(M // 2, N, dtype=torch.bfloat16, device="cuda")
-    ctx.convert_f32_clear(t1.data_ptr(), out.data_ptr(), out.numel(), "bf16", stream=s)
+    out = torch.empty(rows, N, dtype=torch.bfloat16, device="cuda")
+    ctx.sum_slots(owners[1].data_ptr(), 2, rows * N, out.data_ptr(), rows * N, "bf16", stream=s)
     torch.cuda.synchronize()
-    assert rel_frobenius(from_storage(to_host(out, "bf16"), "bf16"), ref[M // 2:]) <= TOL["bf16"]
-    assert not t1.any()
+    assert rel_frobenius(from_storage(to_host(out, "bf16"), "bf16"), ref[rows:]) <= TOL["bf16"]
+    want = (owners[1][0] + owners[1][1]).to(torch.bfloat16)
+    assert torch.equal(out, want)  # slot order, one rounding
     with pytest.raises(ValueError):
-        ctx.gemm_push(desc, da.data_ptr(), db.data_ptr(), [t0.data_ptr()], M // 4, N, stream=s)  # rows not covered
+        ctx.gemm_push(desc, da.data_ptr(), db.data_ptr(), [owners[0][0].data_ptr()], M // 4, N, stream=s)  # rows not covered
 
 
-def test_gemm_push_tail_wave_k_halves(ctx):
-    # 80 tiles on 74 CTA pairs: the last wave's tiles run as K halves that both add into the target
+def test_gemm_push_more_tiles_than_cta_pairs(ctx):
+    # 80 tiles on 74 CTA pairs, four owners: every tile is stored whole (no K halves in this mode)
     import torch
     M, N, K = 2048, 2560, 512
     a, b = inputs.gemm_inputs(M, N, K, "fp16", False, True, 63, "normal_rsqrt_k")
     da, db = to_device(a, "fp16"), to_device(b, "fp16")
-    t = [torch.zeros(M // 4, N, device="cuda") for _ in range(4)]
+    t = [torch.full((M // 4, N), float("nan"), device="cuda") for _ in range(4)]
     desc = capi.gemm_desc(M, N, K, "fp16", "fp32", False, True, clear_accum=True, algo=capi.ALGO_TCGEN05_PAIR)
     s = torch.cuda.current_stream().cuda_stream
     ctx.gemm_push(desc, da.data_ptr(), db.data_ptr(), [x.data_ptr() for x in t], M // 4, N, stream=s)
