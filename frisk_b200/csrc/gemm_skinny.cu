@@ -49,7 +49,7 @@ struct SkinnyPlan {
   int kslice;       // elements per split (multiple of kChunkK)
   int ngroups;      // ceil(N / 8)
   size_t smem;      // dynamic shared bytes
-  size_t off_tickets, off_partials, ws_bytes;
+  size_t off_partials, ws_bytes;
   int grid;
 };
 
@@ -114,7 +114,7 @@ template <typename T, typename TO>
 __global__ void __launch_bounds__(kThreads, 1)
     gemm_skinny_kernel(const T* __restrict__ X, const T* __restrict__ W, TO* __restrict__ Y, int M, int N,
                        int K, int64_t ldx, int64_t ldw, int64_t ldy, int S, int kslice, int ngroups,
-                       int accumulate, unsigned* __restrict__ ctl, unsigned* __restrict__ tickets,
+                       int accumulate, unsigned* __restrict__ ctl,
                        float* __restrict__ partials) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -314,9 +314,7 @@ SkinnyPlan make_plan(const frisk_b200_gemm_desc& d, int num_sms) {
   p.smem = smem_of(S);
   p.grid = (num_sms / S) * S;
   if (p.grid < S) p.grid = S;
-  p.off_tickets = kCtlInts * sizeof(unsigned);
-  size_t tick_bytes = ((size_t)p.ngroups * sizeof(unsigned) + 255) / 256 * 256;
-  p.off_partials = p.off_tickets + tick_bytes;
+  p.off_partials = kCtlInts * sizeof(unsigned);  // queue counters, then the fp32 partials
   p.ws_bytes = p.off_partials + (S > 1 ? (size_t)S * 16 * p.ngroups * 8 * sizeof(float) : 0);
   return p;
 }
@@ -333,7 +331,6 @@ int launch_typed(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc& d, const Skinn
   kern<<<p.grid, kThreads, p.smem, s>>>(static_cast<const T*>(A), static_cast<const T*>(B), static_cast<TO*>(C),
                                         (int)g.M, (int)g.N, (int)g.K, g.lda, g.ldb, g.ldc, p.S, p.kslice,
                                         p.ngroups, d.clear_accum ? 0 : 1, reinterpret_cast<unsigned*>(w),
-                                        reinterpret_cast<unsigned*>(w + p.off_tickets),
                                         reinterpret_cast<float*>(w + p.off_partials));
   FB_CUDA(ctx, cudaGetLastError());
   if (p.S > 1) {
@@ -447,7 +444,7 @@ extern "C" int frisk_b200_gemm_skinny_static(int device, const frisk_b200_gemm_d
   if ((rc = static_scratch_for(device, &scratch))) return rc;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   // The array keeps whatever the previous call (possibly of another shape) left in it:
-  // the counters and tickets at its start must be zero before the kernel runs.
+  // the queue counters at its start must be zero before the kernel runs.
   if (cudaMemsetAsync(scratch, 0, skinny_control_bytes(*desc), s) != cudaSuccess) return FRISK_B200_E_CUDA;
   return launch_gemm_skinny(nullptr, *desc, A, B, C, scratch, kStaticScratchBytes, s);
 }

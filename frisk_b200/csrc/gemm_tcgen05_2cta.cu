@@ -44,6 +44,11 @@ struct Smem2 {
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kBarOffset = kStages2 * kStageBytes;
   static constexpr int kTotal = kBarOffset + 256 + 1024;
+  // push mode only: one [32 rows][32 + 4 floats] transposition buffer per epilogue warp, behind the barriers
+  static constexpr int kPushRowFloats = 36;
+  static constexpr int kPushWarpBytes = 32 * kPushRowFloats * 4;
+  static constexpr int kPushOffset = kBarOffset + 256;
+  static constexpr int kTotalPush = kTotal + 4 * kPushWarpBytes;
 };
 
 // ---- cluster / cta_group::2 primitives
@@ -330,21 +335,37 @@ __global__ void __launch_bounds__(kThreads2, 1)
           }
           const int col = n0 + c * 32;
           if (MODE == kPush) {
-            // split-K across GPUs: store this chunk into this rank's slot at the GPU that owns the row
-            // (plain 16-byte stores; over NVLink they pipeline like a peer copy, remote atomics do not)
-            if (row < M && col < N) {
-              const int owner = row / push.rows_per_target;
-              float* dst = push.ptr[owner] + (int64_t)(row - owner * push.rows_per_target) * push.ld + col;
-              if (col + 32 <= N && (push.ld & 3) == 0) {
+            // split-K across GPUs: store this chunk into this rank's slot at the GPU that owns the row.
+            // A thread holds 32 columns of ONE row; stored as they are, every 16-byte store would be
+            // its own NVLink transaction (measured: 65 GB/s per GPU).  The warp therefore transposes
+            // its 32 x 32 block through shared memory so that eight lanes write one full 128-byte
+            // line of a row and one instruction writes four such lines.
+            float* stage = reinterpret_cast<float*>(smem + L::kPushOffset) + quad * (32 * L::kPushRowFloats);
 #pragma unroll
-                for (int i = 0; i < 8; ++i)
-                  *reinterpret_cast<float4*>(dst + 4 * i) =
-                      make_float4(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]), __uint_as_float(v[4 * i + 2]),
-                                  __uint_as_float(v[4 * i + 3]));
-              } else {
-                for (int i = 0; i < 32 && col + i < N; ++i) dst[i] = __uint_as_float(v[i]);
+            for (int i = 0; i < 8; ++i)
+              *reinterpret_cast<float4*>(stage + lane * L::kPushRowFloats + 4 * i) =
+                  make_float4(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]), __uint_as_float(v[4 * i + 2]),
+                              __uint_as_float(v[4 * i + 3]));
+            __syncwarp();
+            const int piece = lane & 7, rsub = lane >> 3;
+            const int gcol = col + piece * 4;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const int rl = j * 4 + rsub;
+              const int grow = m0 + quad * 32 + rl;
+              const float4 x = *reinterpret_cast<const float4*>(stage + rl * L::kPushRowFloats + piece * 4);
+              if (grow < M && gcol < N) {
+                const int owner = grow / push.rows_per_target;
+                float* dst = push.ptr[owner] + (int64_t)(grow - owner * push.rows_per_target) * push.ld + gcol;
+                if (gcol + 4 <= N && (push.ld & 3) == 0) {
+                  *reinterpret_cast<float4*>(dst) = x;
+                } else {
+                  const float xs[4] = {x.x, x.y, x.z, x.w};
+                  for (int e = 0; e < 4 && gcol + e < N; ++e) dst[e] = xs[e];
+                }
               }
             }
+            __syncwarp();  // the buffer is rewritten for the next 32 columns
           } else if (row < M && col < N) {
             const int valid = min(32, N - col);
             if (MODE == kFused && epi.has_fill) {
@@ -440,7 +461,8 @@ int launch_cfg2(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc& d, const void* 
   if (rc) { ctx->last_cuda = rc; return FRISK_B200_E_CUDA; }
 
   auto kern = gemm_tcgen05_2cta_kernel<TO, BF16, A_MN, B_MN, MODE>;
-  FB_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem2::kTotal));
+  constexpr int kSmemBytes = MODE == kPush ? Smem2::kTotalPush : Smem2::kTotal;
+  FB_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
   cudaLaunchConfig_t cfg = {};
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -448,7 +470,7 @@ int launch_cfg2(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc& d, const void* 
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
   cfg.blockDim = dim3(kThreads2);
-  cfg.dynamicSmemBytes = Smem2::kTotal;
+  cfg.dynamicSmemBytes = kSmemBytes;
   cfg.stream = s;
   cfg.attrs = attr;
   cfg.numAttrs = 1;

@@ -199,3 +199,25 @@ def test_full_size_config(ctx):
         assert rel_frobenius(flat[h][rows], ref[rows]) <= TOL
     # every output row is a convex combination of value rows: bounded by the value range
     assert np.abs(gotf).max() <= np.abs(from_storage(v, "bf16")).max() * 1.01
+
+
+def test_normalized_mode_long_sequence(ctx):
+    """The two-pass mode at the benchmark's sequence length (S = 4096, D = 128, causal, bf16): one head
+    against the strict oracle, which divides by the complete row sum before rounding P."""
+    import torch
+    from oracle.numerics import to_storage
+    rng = np.random.default_rng(13)
+    S, D = 4096, 128
+    q, k, v = (to_storage(rng.standard_normal((1, 1, S, D), dtype=np.float32), "bf16") for _ in range(3))
+    gq, gk, gv = (Guarded(x.shape, "bf16", fill=x) for x in (q, k, v))
+    go = Guarded(q.shape, "fp32")
+    desc = capi.attn_desc(1, 1, S, S, D, D ** -0.5, True, "bf16", "fp32", normalize_p=True)
+    s = torch.cuda.current_stream().cuda_stream
+    ctx.attention_fwd(desc, gq.view.data_ptr(), gk.view.data_ptr(), gv.view.data_ptr(), go.view.data_ptr(), stream=s)
+    ctx.check(s)
+    assert go.guards_intact()
+    ref = ao.attention_fwd(q, k, v, "bf16", D ** -0.5, causal=True, mode="strict")
+    got = go.host()
+    assert np.isfinite(got).all()
+    assert rel_frobenius(got, ref) <= 2e-3
+    assert np.array_equal(got[0, 0, 0], from_storage(v, "bf16")[0, 0, 0])  # query 0 sees only key 0: P = 1 exactly
