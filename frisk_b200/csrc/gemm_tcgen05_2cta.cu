@@ -176,6 +176,12 @@ __global__ void __launch_bounds__(kThreads2, 1)
   cluster_sync_all();  // both CTAs' barriers and tensor memory exist before anything crosses over
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  // Launched with programmatic stream serialization: the next kernel in the stream may take an SM as
+  // soon as this CTA leaves it and run its own set-up (barriers, tensor memory) while our last wave
+  // drains; nothing of that kernel touches global memory before its own wait below has seen the
+  // kernel in front of it complete.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -464,7 +470,9 @@ int launch_cfg2(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc& d, const void* 
   constexpr int kSmemBytes = MODE == kPush ? Smem2::kTotalPush : Smem2::kTotal;
   FB_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
   cudaLaunchConfig_t cfg = {};
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 2;
   attr[0].val.clusterDim.y = 1;
@@ -490,6 +498,7 @@ int launch_cfg2(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc& d, const void* 
     tp.tail_tiles = 0;
   }
   cfg.gridDim = dim3(2 * tp.pairs);
+  cfg.numAttrs = 2;  // (the occupancy query above ran with the cluster attribute alone)
   unsigned* tickets = static_cast<unsigned*>(ws);
   float* partials = tp.tail_tiles ? reinterpret_cast<float*>(static_cast<unsigned char*>(ws) + tp.off_partials) : nullptr;
   int vec_c = aligned16(C) && (g.ldc * sizeof(TO)) % 16 == 0;
