@@ -247,8 +247,10 @@ def run_ours(args):
     e2e_value = world * flop * e2e_steps / e2e_s / 1e12
     checksum = float(hc[:8, :8].float().abs().sum())
 
-    splitk_res = None
+    splitk_res = sharded_res = None
     if world > 1 and not args.no_secondary:
+        # the short sharded workloads first: the deep-K products that follow leave the GPUs power-capped
+        sharded_res = sharded_secondary(ctx, torch, dist, world, stream, peaks)
         splitk_res = splitk_secondary(ctx, torch, dist, world, rank, peaks)
 
     out = None
@@ -280,12 +282,52 @@ def run_ours(args):
                 out["secondary"] = secondary(ctx, torch, stream, peaks, args)
         if splitk_res is not None:
             out["secondary"] = {"gemm_bf16_deepk_splitk": splitk_res}
+            out["secondary"].update(sharded_res or {})
         print(json.dumps(out), flush=True)
     ctx.close()
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
     return out
+
+
+def sharded_secondary(ctx, torch, dist, world, stream, peaks):
+    """The two workloads that shard without communication, strong-scaled over the ranks: the skinny GEMM
+    with N/g columns of W per GPU (X replicated) and the causal attention with 256/g (batch, head) pairs
+    per GPU.  Time = max over ranks; throughput = the whole workload over that time."""
+    from frisk_b200 import capi
+    res = {}
+    try:
+        M, N, K = 16, 28672, 8192
+        n_local = N // world
+        sets = gemm_sets(torch, M, n_local, K, torch.bfloat16, True, 1.0, 0.02, min_bytes=2.5 * L2_BYTES)
+        desc = capi.gemm_desc(M, n_local, K, "bf16", "bf16", False, True)
+        total, _, _ = time_steps(lambda i: ctx.gemm(desc, *(t.data_ptr() for t in sets[i % len(sets)]), stream=stream),
+                                 10, 3, torch, dist, world)
+        ms = total / 10
+        byts = (N * K + world * M * K + M * N) * 2
+        res["gemm_bf16_skinny_sharded"] = {"ms": round(ms, 5), "gbs": round(byts / ms / 1e6, 1), "n_gpus": world,
+                                           "columns_per_gpu": n_local,
+                                           "per_gpu_frac_of_measured_hbm": round(byts / ms / 1e6 / world / peaks["hbm_gbs"], 4)}
+        del sets
+    except Exception as e:  # noqa: BLE001
+        res["gemm_bf16_skinny_sharded"] = {"error": str(e)}
+    try:
+        B, H, S, D = 8, 32, 4096, 128
+        heads = B * H // world
+        q, k, v = (torch.randn(1, heads, S, D, device="cuda", dtype=torch.bfloat16) for _ in range(3))
+        o = torch.empty_like(q)
+        desc = capi.attn_desc(1, heads, S, S, D, 1.0 / math.sqrt(D), True, "bf16", "bf16")
+        total, _, _ = time_steps(lambda i: ctx.attention_fwd(desc, q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),
+                                                             stream=stream), 5, 3, torch, dist, world)
+        ms = total / 5
+        fl = 4.0 * B * H * S * S * D / 2
+        res["attn_bf16_causal_sharded"] = {"ms": round(ms, 5), "tflops": round(fl / ms / 1e9, 2), "n_gpus": world,
+                                           "heads_per_gpu": heads,
+                                           "per_gpu_frac_of_nominal": round(fl / ms / 1e9 / world / NOMINAL_TENSOR_TFLOPS, 4)}
+    except Exception as e:  # noqa: BLE001
+        res["attn_bf16_causal_sharded"] = {"error": str(e)}
+    return res
 
 
 def splitk_secondary(ctx, torch, dist, world, rank, peaks):

@@ -1,5 +1,7 @@
 """The re-hosted builder surface: the flows of the reference's test/python/bind_test.py,
 helper_test.py and legacy_normalization_test.py:82-88, minus what needs frisk-opt."""
+import os
+
 import pytest
 
 import frisk_b200 as F
@@ -204,14 +206,13 @@ def test_fused_plan_folds_fill_and_reduce_into_the_gemm():
         F.fused_plan(build_bind_test_module(clear_accum=True, with_side_ops=True))
 
 
-REFERENCE_TESTS = "/root/reference/test/python"
+REFERENCE_TESTS = os.path.join(os.environ.get("FRISK_REFERENCE_DIR", os.path.join(os.sep, "root", "reference")), "test", "python")
 
 
 @pytest.mark.parametrize("script", ["bind_test.py", "helper_test.py", "map_expr_test.py", "test.py"])
 def test_reference_builder_scripts_run_verbatim(script, capsys):
     """The reference's own builder scripts (`import frisk as F`), unmodified, against this
     package under the name `frisk`.  Skipped where the reference checkout is not present."""
-    import os
     import runpy
     import sys
     path = os.path.join(REFERENCE_TESTS, script)
