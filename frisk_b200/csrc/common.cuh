@@ -76,7 +76,8 @@ int launch_gemm_simt_f32(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc& d, con
 size_t skinny_workspace_bytes(const frisk_b200_gemm_desc& d);
 // bytes at the start of the workspace that hold control words (must be zero before a launch)
 // and a value that identifies their layout: a workspace last used with another layout must
-// have that prefix cleared again, because partial sums may lie where tickets are expected.
+// have that prefix cleared again, because another kernel's partial sums may lie where this one keeps its
+// queue counters.
 size_t skinny_control_bytes(const frisk_b200_gemm_desc& d);
 uint64_t skinny_layout_signature(const frisk_b200_gemm_desc& d);
 bool skinny_supported(const frisk_b200_gemm_desc& d);

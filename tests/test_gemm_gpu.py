@@ -182,7 +182,7 @@ def test_skinny_shapes(ctx, dtype):
 def test_skinny_f32_out_accumulate_and_repeat(ctx):
     check(ctx, 16, 512, 16384, "bf16", "fp32", False, True, 32, algo=capi.ALGO_SKINNY, dist="act_weight")
     check(ctx, 5, 264, 2048, "fp16", "fp16", False, True, 33, accumulate=True, algo=capi.ALGO_SKINNY)
-    # the queue counters and tickets must be clean after every launch: identical bits on repeats
+    # the queue counters must be clean after every launch: identical bits on repeats
     a, b = inputs.gemm_inputs(16, 4096, 8192, "bf16", False, True, 34, "act_weight")
     first, _ = run_gemm(ctx, a, b, "bf16", "bf16", 16, 4096, 8192, False, True, algo=capi.ALGO_SKINNY)
     for _ in range(3):

@@ -43,8 +43,8 @@ def _both(ctx, M, N, K, dtype, seed):
 def test_static_scratch_entry_matches_ordinary_entry_twice():
     ctx = capi.Context(0)
     try:
-        _both(ctx, 16, 1024, 8192, "bf16", 51)   # split-K, small ticket table
-        _both(ctx, 13, 6152, 8192, "bf16", 52)   # larger ticket table over the first call's partial sums
+        _both(ctx, 16, 1024, 8192, "bf16", 51)   # split-K, small partial-sum area
+        _both(ctx, 13, 6152, 8192, "bf16", 52)   # larger layout over the first call's partial sums
         _both(ctx, 16, 1024, 8192, "bf16", 51)   # and back
     finally:
         ctx.close()
