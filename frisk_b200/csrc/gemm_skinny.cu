@@ -302,9 +302,11 @@ SkinnyPlan make_plan(const frisk_b200_gemm_desc& d, int num_sms) {
   while (S < kMaxSplit && smem_of(S) > kMaxSmem) ++S;
   // enough warp-sized work items to keep every warp of the machine busy a few times over
   long want_items = (long)num_sms * kWarps * 4;
-  while (S < kMaxSplit && (long)p.ngroups * S < want_items && slice_of(S + 1) >= 2 * kChunkK &&
-         slice_of(S + 1) < slice_of(S))
-    ++S;
+  // CTAs are bound to a split, so the splits should carry equal work: of the finer splits only those
+  // whose slices cover K without a short last slice are taken
+  auto even = [&](int s) { return (int64_t)slice_of(s) * (s - 1) < d.K && (int64_t)slice_of(s) * s - d.K < kChunkK; };
+  for (int c = S + 1; c <= kMaxSplit && (long)p.ngroups * S < want_items && slice_of(c) >= 2 * kChunkK; ++c)
+    if (even(c) && slice_of(c) < slice_of(S)) S = c;
   if (const char* e = getenv("FRISK_B200_SKINNY_SPLIT")) {
     int v = atoi(e);
     if (v >= 1 && v <= kMaxSplit && smem_of(v) <= kMaxSmem) S = v;
