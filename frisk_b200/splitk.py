@@ -146,6 +146,12 @@ class SplitKGemm:
         return self.out
 
 
+def slot_addresses(owner_bases, rank, slot_elems):
+    """Where rank ``rank`` stores its partial rows: every owner's buffer holds one fp32 slot of
+    ``slot_elems`` elements per rank, in rank order; the result is this rank's slot at every owner."""
+    return [int(base) + rank * slot_elems * 4 for base in owner_bases]
+
+
 class SplitKGemmPush:
     """The same K-split product with the exchange FUSED into the GEMM: the epilogue of the
     tcgen05 kernel stores every finished fp32 tile straight into the memory of the GPU that owns
@@ -181,7 +187,7 @@ class SplitKGemmPush:
             bases = [ptr if r == rank else ctx.peer_buffer_open(handles[r]) for r in range(world)]
             self.own.append(ptr)
             self.mapped.append(bases)
-            self.targets.append([b + rank * self.slot_elems * 4 for b in bases])  # this rank's slot at every owner
+            self.targets.append(slot_addresses(bases, rank, self.slot_elems))
         self.out = torch.empty(self.rows, N, dtype={"bf16": torch.bfloat16, "fp16": torch.float16}[dtype],
                                device=self.device)
         self.token = torch.zeros(1, device=self.device)

@@ -79,3 +79,19 @@ def test_two_rank_gloo_exchange(tmp_path):
     ref = a.double() @ b.double().T
     err = ((full.double() - ref).norm() / ref.norm()).item()
     assert err <= 5e-3
+
+
+def test_push_slot_addresses_do_not_overlap():
+    """Host logic of the fused path: g ranks x g owners, every (owner, rank) slot distinct and inside the owner's buffer."""
+    from frisk_b200 import splitk
+    g, slot_elems = 8, 1024 * 8192
+    bases = [0x7000_0000_0000 + o * (1 << 32) for o in range(g)]
+    seen = set()
+    for rank in range(g):
+        addrs = splitk.slot_addresses(bases, rank, slot_elems)
+        assert len(addrs) == g
+        for owner, a in enumerate(addrs):
+            assert a % 16 == 0 and bases[owner] <= a and a + slot_elems * 4 <= bases[owner] + g * slot_elems * 4
+            assert (owner, a) not in seen
+            seen.add((owner, a))
+    assert len(seen) == g * g
