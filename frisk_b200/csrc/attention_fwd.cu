@@ -34,6 +34,10 @@ namespace {
 using namespace attn;
 
 constexpr int kStagesKV = 2;
+#ifndef FB_ATTN_HEAD_CHUNK
+#define FB_ATTN_HEAD_CHUNK 16
+#endif
+constexpr int kHeadChunk = FB_ATTN_HEAD_CHUNK;
 template <int D>
 struct AttnSmem {
   static constexpr int kTileBytes = BM * D * 2;       // one Q, K or V tile
@@ -69,8 +73,15 @@ __global__ void __launch_bounds__(kThreads, 1)
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int pair = p.n_pairs - 1 - (int)(blockIdx.x % p.n_pairs);  // heavy (late) query tiles first
-  const int bh = (int)(blockIdx.x / p.n_pairs);
+  // CTA order: heads in chunks of kHeadChunk (their K and V stay in L2 together); inside a chunk the
+  // heavy (late) query tiles of every head first, so that the machine drains on light CTAs
+  const int bh_total = (int)(p.total_ctas / p.n_pairs);
+  const int per_chunk = kHeadChunk * p.n_pairs;
+  const int chunk = (int)blockIdx.x / per_chunk;
+  const int within = (int)blockIdx.x - chunk * per_chunk;
+  const int heads_here = min(kHeadChunk, bh_total - chunk * kHeadChunk);
+  const int pair = p.n_pairs - 1 - within / heads_here;
+  const int bh = chunk * kHeadChunk + within % heads_here;
   const int m0 = pair * 2 * BM;
   const int nq[2] = {kv_tiles_for(m0, p.S_q, p.S_kv, p.causal), kv_tiles_for(m0 + BM, p.S_q, p.S_kv, p.causal)};
   const int n_max = max(nq[0], nq[1]);
