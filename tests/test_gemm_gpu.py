@@ -443,3 +443,27 @@ def test_execute_kernel_with_fill_and_reduce(ctx):
     assert rel_frobenius(from_storage(got, "fp16"), ref) <= TOL["fp16"]
     assert np.array_equal(from_storage(to_host(tr, "fp16"), "fp16").astype(np.float64),
                           gemm_oracle.row_reduce(got, "fp16", "max"))
+
+
+def test_fused_epilogue_with_caller_workspace(ctx):
+    """The caller may own the scratch of the fused path: the size the library states is enough, less is refused."""
+    import torch
+    M, N, K = 2304, 2560, 512
+    a, b = inputs.gemm_inputs(M, N, K, "fp16", False, True, 78, "normal_rsqrt_k")
+    da, db = to_device(a, "fp16"), to_device(b, "fp16")
+    dc = torch.empty(M, N, dtype=torch.float16, device="cuda")
+    dr = torch.empty(M, dtype=torch.float16, device="cuda")
+    desc = capi.gemm_desc(M, N, K, "fp16", "fp16", False, True, clear_accum=True)
+    epi = capi.gemm_epilogue(reduce="max", reduce_dst=dr.data_ptr())
+    need = capi.gemm_fused_workspace_bytes(desc, epi)
+    assert need > 0
+    ws = torch.zeros(need, dtype=torch.uint8, device="cuda")
+    s = torch.cuda.current_stream().cuda_stream
+    ctx.gemm_fused(desc, epi, da.data_ptr(), db.data_ptr(), dc.data_ptr(), ws.data_ptr(), need, stream=s)
+    ctx.check(s)
+    got = to_host(dc, "fp16")
+    assert rel_frobenius(from_storage(got, "fp16"), gemm_oracle.gemm_fp64(a, b, "fp16", False, True)) <= TOL["fp16"]
+    assert np.array_equal(from_storage(to_host(dr, "fp16"), "fp16").astype(np.float64),
+                          gemm_oracle.row_reduce(got, "fp16", "max"))
+    with pytest.raises(ValueError):
+        ctx.gemm_fused(desc, epi, da.data_ptr(), db.data_ptr(), dc.data_ptr(), ws.data_ptr(), need - 4096, stream=s)
