@@ -4,10 +4,6 @@
 #include "common.cuh"
 #include "ptx.cuh"
 
-#ifndef FB_ATTN_EMULATE_EVERY
-#define FB_ATTN_EMULATE_EVERY 0
-#endif
-
 namespace fb {
 namespace attn {
 
@@ -17,7 +13,6 @@ constexpr int kThreads = 384;  // warps 0-3, 4-7: softmax groups; warp 8: TMA; w
 constexpr int kRegsSoftmax = 208, kRegsOther = 72;  // per-thread register budgets after setmaxnreg
 constexpr int kWarpTma = 8, kWarpMma = 9;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
-constexpr int kEmulateEvery = FB_ATTN_EMULATE_EVERY;  // 0 = never; 2 = every other pair of P values
 
 enum : unsigned { ST_ATTN_S = 0x201, ST_ATTN_P = 0x202, ST_ATTN_O = 0x203, ST_ATTN_KV = 0x204, ST_ATTN_Q = 0x205 };
 
@@ -56,34 +51,6 @@ __device__ __forceinline__ float2 add2(float2 a, float2 b) {
       : "=l"(*reinterpret_cast<unsigned long long*>(&d))
       : "l"(*reinterpret_cast<unsigned long long*>(&a)), "l"(*reinterpret_cast<unsigned long long*>(&b)));
   return d;
-}
-
-__device__ __forceinline__ float2 add2_rm(float2 a, float2 b) {
-  float2 d;
-  asm("add.rm.ftz.f32x2 %0, %1, %2;"
-      : "=l"(*reinterpret_cast<unsigned long long*>(&d))
-      : "l"(*reinterpret_cast<unsigned long long*>(&a)), "l"(*reinterpret_cast<unsigned long long*>(&b)));
-  return d;
-}
-// 2^x for a pair of values on the FMA/ALU pipes instead of the special-function unit, which is
-// the scarcest resource of the softmax (16 ex2 per clock per SM against 128x128 scores per
-// tile).  x = n + f with n = floor(x) from a round-down add of 1.5*2^23, 2^f from a cubic
-// (max relative error 9e-5, far below the 2^-9 of the 16-bit P it is rounded to), and n is
-// added into the exponent field with integer arithmetic.
-__device__ __forceinline__ float2 ex2_emulated(float2 x) {
-  const float kMagic = 12582912.0f;  // 1.5 * 2^23
-  x.x = fmaxf(x.x, -127.0f);
-  x.y = fmaxf(x.y, -127.0f);
-  const float2 t = add2_rm(x, make_float2(kMagic, kMagic));
-  const float2 nf = add2(t, make_float2(-kMagic, -kMagic));
-  const float2 f = fma2(nf, make_float2(-1.0f, -1.0f), x);
-  float2 r = fma2(f, make_float2(0.077119089663028717f, 0.077119089663028717f),
-                  make_float2(0.227564394474029541f, 0.227564394474029541f));
-  r = fma2(r, f, make_float2(0.695146143436431885f, 0.695146143436431885f));
-  r = fma2(r, f, make_float2(1.0f, 1.0f));
-  r.x = __int_as_float(__float_as_int(r.x) + (__float_as_int(t.x) << 23));
-  r.y = __int_as_float(__float_as_int(r.y) + (__float_as_int(t.y) << 23));
-  return r;
 }
 
 template <bool BF16>

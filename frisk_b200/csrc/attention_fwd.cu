@@ -413,9 +413,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
           float2 x = fma2(make_float2(__uint_as_float(sr[c][2 * i]), __uint_as_float(sr[c][2 * i + 1])), scale2, negm2);
-          // every kEmulateEvery-th pair goes to the FMA pipes, the rest to the SFU
-          float2 e = (kEmulateEvery > 0 && (i % kEmulateEvery) == kEmulateEvery - 1) ? ex2_emulated(x)
-                                                                                  : make_float2(ex2f(x.x), ex2f(x.y));
+          float2 e = make_float2(ex2f(x.x), ex2f(x.y));
           if (i & 1) sum_b = add2(sum_b, e); else sum_a = add2(sum_a, e);
           pk[i] = pack16<BF16>(e.x, e.y);
         }

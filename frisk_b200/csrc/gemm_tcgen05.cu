@@ -32,7 +32,6 @@ constexpr int BK = 64;       // one 128-byte swizzle span of 16-bit elements
 constexpr int UMMA_K = 16;
 constexpr int kStages = 4;
 constexpr int kThreads = 192;
-constexpr int kEpiWarp0 = 2;
 // k-blocks between an optional L2 prefetch and the shared-memory load.  Measured on B200 at
 // 4096^3: 0 (off) 1250 TFLOP/s, 2: 946, 4: 952, 16: 1016 -- the prefetches compete with the
 // loads for the TMA unit, so it stays off; FRISK_B200_GEMM_PREFETCH overrides for experiments.
