@@ -109,8 +109,10 @@ def fused_plan(module_or_kernel, name=None, algo=capi.ALGO_AUTO):
     the kernel arguments bound to A, B and C and ``epilogue`` is None or a dict with ``fill``
     (value or None), ``reduce`` (kind or None), ``reduce_arg`` (argument index) and ``reduce_clear``."""
     kernel = _kernel_of(module_or_kernel, name)
-    if not kernel.verify():
-        raise ValueError("frisk-b200-execute: kernel does not verify")
+    try:
+        ir._verify(kernel)
+    except ValueError as e:
+        raise ValueError(f"frisk-b200-execute: kernel does not verify: {e}") from None
     gemm, chain, fill, reduce = _find_gemm(kernel)
     entry = kernel.regions[0].front()
     idx = []
@@ -147,6 +149,11 @@ def fused_plan(module_or_kernel, name=None, algo=capi.ALGO_AUTO):
                 raise ValueError("frisk-b200-execute: the reduce destination must be a global kernel argument")
             if reduce.attrs["kind"] not in ("max", "min", "add"):
                 raise ValueError(f"frisk-b200-execute: no kernel for reduce kind {reduce.attrs['kind']}")
+            # the row-reduction kernels write M elements of C's element type (the verifier has
+            # already required exactly that of the destination memref; checked again because an
+            # undersized buffer here would be a device-side out-of-bounds write)
+            if list(dst.type.shape) != [a["M"]] or dst.type.element != tc.element:
+                raise ValueError("frisk-b200-execute: the reduce destination must be memref<M x element type of C>")
             epilogue.update(reduce=reduce.attrs["kind"], reduce_arg=dst.index, reduce_clear=bool(reduce.attrs["clear"]))
     return desc, tuple(idx), epilogue
 

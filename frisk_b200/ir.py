@@ -710,6 +710,25 @@ def _verify(op):
         if op.operands[0].type.element != op.attrs["value"][1]:
             raise ValueError(f"value type {op.attrs['value'][1]} does not match memref element type "
                              f"{op.operands[0].type.element}")
+    elif isinstance(op, ReduceOp):  # FriskOps.cpp:728-762
+        src, dst = op.operands[0].type, op.operands[1].type
+        kind, dim = op.attrs["kind"], op.attrs["dim"]
+        if src.kind != "memref" or dst.kind != "memref":
+            raise ValueError("source and destination must be memref types")
+        if dim < 0 or dim >= len(src.shape):
+            raise ValueError(f"dimension {dim} is out of range for source of rank {len(src.shape)}")
+        if kind not in ("add", "mul", "min", "max"):
+            raise ValueError(f"unsupported reduce kind: {kind}. Supported: add, mul, min, max")
+        if len(src.shape) != len(dst.shape) + 1:
+            raise ValueError("destination rank must be one less than source rank. Got: "
+                             f"{len(dst.shape)} vs {len(src.shape)}")
+        kept = [i for i in range(len(src.shape)) if i != dim]
+        for j, i in enumerate(kept):
+            if src.shape[i] != dst.shape[j]:
+                raise ValueError(f"non-reduced dimension mismatch: source[{i}] = {src.shape[i]} vs "
+                                 f"destination[{j}] = {dst.shape[j]}")
+        if src.element != dst.element:
+            raise ValueError("source and destination must have the same element type")
     elif isinstance(op, CopyOp):  # FriskOps.cpp:662-679
         if len(op.get_src_indices()) != op.attrs["srcMap"].get_num_inputs():
             raise ValueError("source index count does not match the source map")

@@ -48,7 +48,9 @@ def load_tile_reference(ref_root):
 
 
 def main():
-    ref_root = pathlib.Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        raise SystemExit("usage: python tests/golden/make_golden.py /path/to/reference")
+    ref_root = pathlib.Path(sys.argv[1])
     tail = load_tail(ref_root)
 
     tiled = {}

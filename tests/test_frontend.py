@@ -160,7 +160,8 @@ def test_execute_refuses_cpu_tensors():
         F.execute(mod, t, t, t.clone(), v)
 
 
-def build_fused_module(fill=None, reduce=None, clear=True, clear_accum=False, shape=(512, 384, 256), trips=1):
+def build_fused_module(fill=None, reduce=None, clear=True, clear_accum=False, shape=(512, 384, 256), trips=1,
+                       r_shape=None, r_type=None, dim=1):
     """kernel(A[M,K], B[N,K], C[M,N], r[M]): parallel { for { [fill C] gemm(A, B^T, C) [reduce C -> r] } }"""
     m, n, k = shape
     context = F.context()
@@ -169,7 +170,10 @@ def build_fused_module(fill=None, reduce=None, clear=True, clear_accum=False, sh
     module = builder.create_module()
     module.context = context
     f16 = builder.get_f16_ty()
-    types = [builder.get_memref_ty(f16, s, F.AffineMap(), F.MemorySpace.GLOBAL) for s in ([m, k], [n, k], [m, n], [m])]
+    types = [builder.get_memref_ty(f16, s, F.AffineMap(), F.MemorySpace.GLOBAL) for s in ([m, k], [n, k], [m, n])]
+    r_elem = f16 if r_type is None else getattr(builder, f"get_{r_type}_ty")()
+    types.append(builder.get_memref_ty(r_elem, [m] if r_shape is None else list(r_shape), F.AffineMap(),
+                                       F.MemorySpace.GLOBAL))
     kernel = builder.create_kernel_op(module, "fused", builder.get_kernel_ty(types))
     module.push_back(kernel)
     entry = kernel.add_entry_block()
@@ -183,9 +187,38 @@ def build_fused_module(fill=None, reduce=None, clear=True, clear_accum=False, sh
             builder.create_fill_op(c, fill, "fp16")
         builder.create_gemm_op(a, b, c, False, True, clear_accum)
         if reduce is not None:
-            builder.create_reduce_op(c, r, reduce, 1, clear)
+            builder.create_reduce_op(c, r, reduce, dim, clear)
     builder.create_for_op(0, trips, 1, body)
     return module
+
+
+@pytest.mark.parametrize("kwargs,message", [
+    (dict(r_shape=[8]), r"non-reduced dimension mismatch: source\[0\] = 512 vs destination\[0\] = 8"),
+    (dict(r_type="f32"), "source and destination must have the same element type"),
+    (dict(r_shape=[512, 1]), "destination rank must be one less than source rank. Got: 2 vs 2"),
+    (dict(dim=2), "dimension 2 is out of range for source of rank 2"),
+    (dict(dim=-1), "dimension -1 is out of range for source of rank 2"),
+    (dict(reduce="xor"), "unsupported reduce kind: xor. Supported: add, mul, min, max"),
+])
+def test_reduce_verifier_rejects_what_the_reference_rejects(kwargs, message):
+    """ReduceOp::verify (lib/Dialect/Frisk/IR/FriskOps.cpp:728-762): a destination whose rank, kept
+    extents or element type disagree with the source never reaches a kernel."""
+    kw = dict(reduce="max", clear_accum=True)
+    kw.update(kwargs)
+    mod = build_fused_module(**kw)
+    assert not mod.verify()
+    with pytest.raises(ValueError, match=message):
+        F.ir._verify(mod)
+    with pytest.raises(ValueError, match="does not verify"):
+        F.fused_plan(mod)
+
+
+def test_reduce_verifier_accepts_the_reduction_along_dim_0():
+    # dim 0 of an M x N source keeps N: verifies, but has no kernel here
+    mod = build_fused_module(reduce="max", clear_accum=True, dim=0, shape=(384, 384, 256))
+    assert mod.verify()
+    with pytest.raises(ValueError, match="unsupported op frisk.reduce"):
+        F.fused_plan(mod)
 
 
 def test_fused_plan_folds_fill_and_reduce_into_the_gemm():
@@ -206,7 +239,16 @@ def test_fused_plan_folds_fill_and_reduce_into_the_gemm():
         F.fused_plan(build_bind_test_module(clear_accum=True, with_side_ops=True))
 
 
-REFERENCE_TESTS = os.path.join(os.environ.get("FRISK_REFERENCE_DIR", os.path.join(os.sep, "root", "reference")), "test", "python")
+def _reference_dir():
+    """FRISK_REFERENCE_DIR, else a checkout named `reference` beside this repository."""
+    env = os.environ.get("FRISK_REFERENCE_DIR")
+    if env:
+        return env
+    repo = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    return os.path.join(os.path.dirname(repo), "reference")
+
+
+REFERENCE_TESTS = os.path.join(_reference_dir(), "test", "python")
 
 
 @pytest.mark.parametrize("script", ["bind_test.py", "helper_test.py", "map_expr_test.py", "test.py"])
