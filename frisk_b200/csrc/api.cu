@@ -150,7 +150,10 @@ int launch_convert_f32(const float* src, void* dst, int64_t n, int dtype, cudaSt
 // ---------------------------------------------------------------- helpers
 namespace {
 
-int ensure_stage(frisk_b200_ctx* ctx, int slot, size_t bytes, bool zero) {
+// (Re)allocates a context-owned buffer.  `zero`: fresh memory is cleared ON `s`, the stream
+// the kernel that needs the zeroed control words is launched on (a clear on the legacy
+// default stream would not be ordered before a kernel on a non-blocking stream).
+int ensure_stage(frisk_b200_ctx* ctx, int slot, size_t bytes, bool zero, cudaStream_t s = nullptr) {
   StagingBuffer& b = ctx->stage[slot];
   if (b.bytes >= bytes && b.ptr) return 0;
   if (b.ptr) {
@@ -161,7 +164,7 @@ int ensure_stage(frisk_b200_ctx* ctx, int slot, size_t bytes, bool zero) {
   size_t want = (bytes + 255) / 256 * 256;
   FB_CUDA(ctx, cudaMalloc(&b.ptr, want));
   b.bytes = want;
-  if (zero) FB_CUDA(ctx, cudaMemset(b.ptr, 0, want));
+  if (zero) FB_CUDA(ctx, cudaMemsetAsync(b.ptr, 0, want, s));
   return 0;
 }
 
@@ -170,7 +173,7 @@ int ensure_stage(frisk_b200_ctx* ctx, int slot, size_t bytes, bool zero) {
 int prepare_owned_skinny_ws(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc& d, cudaStream_t s) {
   size_t need = skinny_workspace_bytes(d);
   void* before = ctx->stage[3].ptr;
-  int rc = ensure_stage(ctx, 3, need, true);
+  int rc = ensure_stage(ctx, 3, need, true, s);
   if (rc) return rc;
   uint64_t sig = skinny_layout_signature(d);
   if (ctx->stage[3].ptr != before) {
@@ -180,29 +183,6 @@ int prepare_owned_skinny_ws(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc& d, 
     ctx->ws_signature = sig;
   }
   return 0;
-}
-
-bool ranges_overlap(const void* a, size_t an, const void* b, size_t bn) {
-  uintptr_t a0 = reinterpret_cast<uintptr_t>(a), b0 = reinterpret_cast<uintptr_t>(b);
-  return a0 < b0 + bn && b0 < a0 + an;
-}
-
-size_t operand_bytes(int64_t rows, int64_t cols, int64_t ld, size_t es) {
-  if (rows <= 0) return 0;
-  return (size_t)((rows - 1) * ld + cols) * es;
-}
-
-struct GemmExtents {
-  size_t a, b, c;
-};
-GemmExtents gemm_extents(const frisk_b200_gemm_desc& d) {
-  GemmDims g = resolve_dims(d);
-  size_t es = dtype_size(d.dtype_ab), cs = dtype_size(d.dtype_c);
-  GemmExtents e;
-  e.a = d.trans_a ? operand_bytes(g.K, g.M, g.lda, es) : operand_bytes(g.M, g.K, g.lda, es);
-  e.b = d.trans_b ? operand_bytes(g.N, g.K, g.ldb, es) : operand_bytes(g.K, g.N, g.ldb, es);
-  e.c = operand_bytes(g.M, g.N, g.ldc, cs);
-  return e;
 }
 
 }  // namespace
@@ -245,7 +225,8 @@ int frisk_b200_ctx_create(frisk_b200_ctx** out, int device) {
     return FRISK_B200_E_CUDA;
   };
   cudaError_t e;
-  if ((e = cudaSetDevice(device)) != cudaSuccess) return fail(e);
+  DeviceGuard guard(device);  // the caller's current device is put back on return
+  if ((e = guard.error()) != cudaSuccess) return fail(e);
   cudaDeviceProp prop;
   if ((e = cudaGetDeviceProperties(&prop, device)) != cudaSuccess) return fail(e);
   if (prop.major != 10) {  // sm_100a code only: fail loudly on anything else
@@ -268,7 +249,7 @@ int frisk_b200_ctx_create(frisk_b200_ctx** out, int device) {
 
 int frisk_b200_ctx_destroy(frisk_b200_ctx* ctx) {
   if (!ctx) return FRISK_B200_E_ARG;
-  cudaSetDevice(ctx->device);
+  DeviceGuard guard(ctx->device);
   cudaDeviceSynchronize();
   for (auto& b : ctx->stage)
     if (b.ptr) cudaFree(b.ptr);
@@ -385,7 +366,7 @@ int frisk_b200_gemm(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc* d, const vo
   GemmExtents e = gemm_extents(*d);
   if (ranges_overlap(C, e.c, A, e.a) || ranges_overlap(C, e.c, B, e.b)) return FRISK_B200_E_OVERLAP;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  FB_CUDA(ctx, cudaSetDevice(ctx->device));
+  FB_DEVICE(ctx);
   switch (algo) {
     case FRISK_B200_ALGO_SIMT_F32:
       return launch_gemm_simt_f32(ctx, *d, static_cast<const float*>(A), static_cast<const float*>(B),
@@ -410,7 +391,7 @@ int frisk_b200_gemm(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc* d, const vo
       if (need && !workspace) {
         // library-owned scratch: zeroed when allocated, tickets are left at zero by every launch
         std::lock_guard<std::mutex> lock(ctx->mu);
-        int rc = ensure_stage(ctx, 5, need, true);
+        int rc = ensure_stage(ctx, 5, need, true, s);
         if (rc) return rc;
         workspace = ctx->stage[5].ptr;
         workspace_bytes = ctx->stage[5].bytes;
@@ -426,7 +407,7 @@ int frisk_b200_gemm_host(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc* d, con
   if (!ctx || !d || !A || !B || !C) return FRISK_B200_E_ARG;
   int algo = frisk_b200_gemm_select(d);
   if (algo < 0) return algo;
-  FB_CUDA(ctx, cudaSetDevice(ctx->device));
+  FB_DEVICE(ctx);
   GemmExtents e = gemm_extents(*d);
   std::lock_guard<std::mutex> lock(ctx->mu);
   int rc;
@@ -436,7 +417,7 @@ int frisk_b200_gemm_host(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc* d, con
   cudaStream_t s = ctx->host_stream, s2 = ctx->copy_stream, s3 = ctx->out_stream;
   if (algo == FRISK_B200_ALGO_SKINNY && (rc = prepare_owned_skinny_ws(ctx, *d, s))) return rc;
   if (size_t need = (algo == FRISK_B200_ALGO_TCGEN05_PAIR ? tcgen05_2cta_workspace_bytes(*d) : 0))
-    if ((rc = ensure_stage(ctx, 5, need, true))) return rc;
+    if ((rc = ensure_stage(ctx, 5, need, true, s))) return rc;
   GemmDims g = resolve_dims(*d);
   const size_t es = dtype_size(d->dtype_ab), cs = dtype_size(d->dtype_c);
 
@@ -444,23 +425,22 @@ int frisk_b200_gemm_host(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc* d, con
   // kernels on a second, D2H on a third, ordered by events (PCIe is full duplex, so the
   // copy-out of panel p overlaps the copy-in of panel p+1).  Only when A's rows are
   // contiguous in the buffer (trans_a = 0) and the problem is large enough to split.
-  // Panel boundaries (rows, multiples of 256).  Measured on the 4096^3 fp16 product: 1 panel 1.92 ms,
-  // 2: 1.65, 4: 1.57, 6: 1.59, 8: 1.64 (per-copy overheads), 4 panels shrinking towards the end 1.59.
-  int64_t bounds[12] = {0};
+  // Panel boundaries are multiples of 256 rows; four panels (more only add per-copy overheads).
+  // Every panel runs the kernel chosen for the WHOLE problem (its scratch is the one prepared
+  // above, and an explicit desc->algo is honoured); a last panel shorter than 256 rows is
+  // merged into the one before it.
+  int64_t bounds[8] = {0};
   int panels = 1;
   bounds[1] = g.M;
   if (!d->trans_a && algo != FRISK_B200_ALGO_SKINNY && g.M >= 1024 && e.a + e.c >= ((size_t)8 << 20)) {
-    int want = 4;
-    if (const char* env = getenv("FRISK_B200_HOST_PANELS")) {
-      const int v = atoi(env);
-      if (v >= 1 && v <= 11) want = v;
-    }
+    constexpr int want = 4;
     panels = 0;
     for (int i = 0; i < want; ++i) {
       int64_t end = g.M * (i + 1) / want;
       end = i + 1 == want ? g.M : std::min<int64_t>(g.M, (end + 255) / 256 * 256);
       if (end > bounds[panels]) bounds[++panels] = end;
     }
+    if (panels > 1 && bounds[panels] - bounds[panels - 1] < 256) bounds[--panels] = g.M;
   }
 
   FB_CUDA(ctx, cudaMemcpyAsync(ctx->stage[1].ptr, B, e.b, cudaMemcpyHostToDevice, s2));
@@ -471,9 +451,8 @@ int frisk_b200_gemm_host(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc* d, con
     dp.lda = g.lda;
     dp.ldb = g.ldb;
     dp.ldc = g.ldc;
-    dp.algo = FRISK_B200_ALGO_AUTO;
-    const int algo_p = panels == 1 ? algo : frisk_b200_gemm_select(&dp);
-    if (algo_p < 0) return algo_p;
+    dp.algo = algo;
+    const int algo_p = algo;
     // with trans_a the single panel is the whole (K x M) buffer
     const size_t a_off = d->trans_a ? 0 : (size_t)r0 * g.lda * es, a_bytes = panels == 1 ? e.a : operand_bytes(rows, g.K, g.lda, es);
     const size_t c_off = (size_t)r0 * g.ldc * cs, c_bytes = operand_bytes(rows, g.N, g.ldc, cs);
@@ -548,7 +527,7 @@ int frisk_b200_attention_fwd(frisk_b200_ctx* ctx, const frisk_b200_attn_desc* d,
     return FRISK_B200_E_OVERLAP;
   for (const void* p : {Q, K, V, (const void*)O})
     if (reinterpret_cast<uintptr_t>(p) & 15u) return FRISK_B200_E_ALIGN;
-  FB_CUDA(ctx, cudaSetDevice(ctx->device));
+  FB_DEVICE(ctx);
   return launch_attention_fwd(ctx, *d, Q, K, V, O, static_cast<cudaStream_t>(stream));
 }
 
@@ -557,7 +536,7 @@ int frisk_b200_attention_fwd_host(frisk_b200_ctx* ctx, const frisk_b200_attn_des
   if (!ctx || !d || !Q || !K || !V || !O) return FRISK_B200_E_ARG;
   int rc = frisk_b200_attention_validate(d);
   if (rc) return rc;
-  FB_CUDA(ctx, cudaSetDevice(ctx->device));
+  FB_DEVICE(ctx);
   size_t es = dtype_size(d->dtype_in), os = dtype_size(d->dtype_out);
   size_t qb = (size_t)d->B * d->H * d->S_q * d->D * es, kb = (size_t)d->B * d->H * d->S_kv * d->D * es;
   size_t ob = (size_t)d->B * d->H * d->S_q * d->D * os;
@@ -604,7 +583,7 @@ int frisk_b200_gemm_push(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc* d, con
   push.n = n_targets;
   push.rows_per_target = (int)rows_per_target;
   push.ld = ld_target;
-  FB_CUDA(ctx, cudaSetDevice(ctx->device));
+  FB_DEVICE(ctx);
   return launch_gemm_tcgen05_2cta_push(ctx, *d, A, B, push, static_cast<cudaStream_t>(stream));
 }
 
@@ -656,7 +635,7 @@ int frisk_b200_gemm_fused(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc* d, co
        ranges_overlap(e->reduce_dst, (size_t)g.M * cs, B, ext.b)))
     return FRISK_B200_E_OVERLAP;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  FB_CUDA(ctx, cudaSetDevice(ctx->device));
+  FB_DEVICE(ctx);
   const bool use_fill = e->fill_enable && !d->clear_accum;  // a fill before an overwriting gemm is dead
   const float fill = round_fill(e->fill_value, d->dtype_c);
   if (fused == 0) {
@@ -681,7 +660,7 @@ int frisk_b200_gemm_fused(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc* d, co
     std::lock_guard<std::mutex> lock(ctx->mu);
     int rc;
     if (tail) {
-      if ((rc = ensure_stage(ctx, 5, tail, true))) return rc;
+      if ((rc = ensure_stage(ctx, 5, tail, true, s))) return rc;
       ws_tail = ctx->stage[5].ptr;
       ws_tail_bytes = ctx->stage[5].bytes;
     }
@@ -706,7 +685,7 @@ int frisk_b200_gemm_fused(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc* d, co
 int frisk_b200_sum_slots(frisk_b200_ctx* ctx, const float* slots, int32_t n_slots, int64_t slot_elems, void* dst,
                          int64_t count, int32_t dtype_dst, void* stream) {
   if (!ctx || !slots || !dst || count < 0 || n_slots < 1 || slot_elems < count) return FRISK_B200_E_ARG;
-  FB_CUDA(ctx, cudaSetDevice(ctx->device));
+  FB_DEVICE(ctx);
   return launch_sum_slots(slots, n_slots, slot_elems, dst, count, dtype_dst, static_cast<cudaStream_t>(stream));
 }
 
@@ -714,10 +693,11 @@ int frisk_b200_sum_slots(frisk_b200_ctx* ctx, const float* slots, int32_t n_slot
 int frisk_b200_peer_buffer_create(frisk_b200_ctx* ctx, size_t bytes, void** ptr, void* handle64) {
   if (!ctx || !ptr || !handle64 || bytes == 0) return FRISK_B200_E_ARG;
   static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle is 64 bytes");
-  FB_CUDA(ctx, cudaSetDevice(ctx->device));
+  FB_DEVICE(ctx);
   void* p = nullptr;
   FB_CUDA(ctx, cudaMalloc(&p, bytes));
   cudaError_t e = cudaMemset(p, 0, bytes);
+  if (e == cudaSuccess) e = cudaDeviceSynchronize();  // zero before the handle leaves this process
   cudaIpcMemHandle_t h;
   if (e == cudaSuccess) e = cudaIpcGetMemHandle(&h, p);
   if (e != cudaSuccess) {
@@ -731,7 +711,7 @@ int frisk_b200_peer_buffer_create(frisk_b200_ctx* ctx, size_t bytes, void** ptr,
 }
 int frisk_b200_peer_buffer_open(frisk_b200_ctx* ctx, const void* handle64, void** ptr) {
   if (!ctx || !ptr || !handle64) return FRISK_B200_E_ARG;
-  FB_CUDA(ctx, cudaSetDevice(ctx->device));
+  FB_DEVICE(ctx);
   cudaIpcMemHandle_t h;
   memcpy(&h, handle64, sizeof(h));
   FB_CUDA(ctx, cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess));
@@ -739,7 +719,7 @@ int frisk_b200_peer_buffer_open(frisk_b200_ctx* ctx, const void* handle64, void*
 }
 int frisk_b200_peer_buffer_close(frisk_b200_ctx* ctx, void* ptr, int32_t owned) {
   if (!ctx || !ptr) return FRISK_B200_E_ARG;
-  FB_CUDA(ctx, cudaSetDevice(ctx->device));
+  FB_DEVICE(ctx);
   if (owned) FB_CUDA(ctx, cudaFree(ptr)); else FB_CUDA(ctx, cudaIpcCloseMemHandle(ptr));
   return 0;
 }
@@ -747,7 +727,7 @@ int frisk_b200_peer_buffer_close(frisk_b200_ctx* ctx, void* ptr, int32_t owned) 
 int frisk_b200_convert_f32(frisk_b200_ctx* ctx, const float* src, void* dst, int64_t count, int32_t dtype_dst,
                            void* stream) {
   if (!ctx || !src || !dst || count < 0) return FRISK_B200_E_ARG;
-  FB_CUDA(ctx, cudaSetDevice(ctx->device));
+  FB_DEVICE(ctx);
   return launch_convert_f32(src, dst, count, dtype_dst, static_cast<cudaStream_t>(stream));
 }
 

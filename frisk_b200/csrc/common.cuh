@@ -57,6 +57,33 @@ inline bool dtype_ok(int dt) { return dt == FRISK_B200_F32 || dt == FRISK_B200_F
     }                                               \
   } while (0)
 
+// Makes `device` current for the duration of an entry point and puts the caller's device back
+// when it returns, so that a call never changes the calling thread's current device.
+class DeviceGuard {
+ public:
+  explicit DeviceGuard(int device) {
+    err_ = cudaGetDevice(&prev_);
+    if (err_ == cudaSuccess && prev_ != device) {
+      err_ = cudaSetDevice(device);
+      switched_ = err_ == cudaSuccess;
+    }
+  }
+  ~DeviceGuard() {
+    if (switched_) cudaSetDevice(prev_);
+  }
+  DeviceGuard(const DeviceGuard&) = delete;
+  DeviceGuard& operator=(const DeviceGuard&) = delete;
+  cudaError_t error() const { return err_; }
+
+ private:
+  int prev_ = 0;
+  bool switched_ = false;
+  cudaError_t err_ = cudaSuccess;
+};
+#define FB_DEVICE(ctx)                   \
+  fb::DeviceGuard device_guard__((ctx)->device); \
+  FB_CUDA(ctx, device_guard__.error())
+
 // resolved leading dimensions (elements)
 struct GemmDims {
   int64_t M, N, K, lda, ldb, ldc;
@@ -68,6 +95,31 @@ inline GemmDims resolve_dims(const frisk_b200_gemm_desc& d) {
   if (g.ldc == 0) g.ldc = d.N;
   return g;
 }
+
+// ---- byte extents of the operands, for the output-overlaps-input refusal every entry makes
+inline bool ranges_overlap(const void* a, size_t an, const void* b, size_t bn) {
+  uintptr_t a0 = reinterpret_cast<uintptr_t>(a), b0 = reinterpret_cast<uintptr_t>(b);
+  return a0 < b0 + bn && b0 < a0 + an;
+}
+
+inline size_t operand_bytes(int64_t rows, int64_t cols, int64_t ld, size_t es) {
+  if (rows <= 0) return 0;
+  return (size_t)((rows - 1) * ld + cols) * es;
+}
+
+struct GemmExtents {
+  size_t a, b, c;
+};
+inline GemmExtents gemm_extents(const frisk_b200_gemm_desc& d) {
+  GemmDims g = resolve_dims(d);
+  size_t es = dtype_size(d.dtype_ab), cs = dtype_size(d.dtype_c);
+  GemmExtents e;
+  e.a = d.trans_a ? operand_bytes(g.K, g.M, g.lda, es) : operand_bytes(g.M, g.K, g.lda, es);
+  e.b = d.trans_b ? operand_bytes(g.N, g.K, g.ldb, es) : operand_bytes(g.K, g.N, g.ldb, es);
+  e.c = operand_bytes(g.M, g.N, g.ldc, cs);
+  return e;
+}
+
 
 // ---- kernel launchers (one per .cu file) --------------------------------------------
 int launch_gemm_simt_f32(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc& d, const float* A, const float* B,

@@ -307,10 +307,6 @@ SkinnyPlan make_plan(const frisk_b200_gemm_desc& d, int num_sms) {
   auto even = [&](int s) { return (int64_t)slice_of(s) * (s - 1) < d.K && (int64_t)slice_of(s) * s - d.K < kChunkK; };
   for (int c = S + 1; c <= kMaxSplit && (long)p.ngroups * S < want_items && slice_of(c) >= 2 * kChunkK; ++c)
     if (even(c) && slice_of(c) < slice_of(S)) S = c;
-  if (const char* e = getenv("FRISK_B200_SKINNY_SPLIT")) {
-    int v = atoi(e);
-    if (v >= 1 && v <= kMaxSplit && smem_of(v) <= kMaxSmem) S = v;
-  }
   p.S = S;
   p.kslice = slice_of(S);
   p.smem = smem_of(S);
@@ -363,6 +359,9 @@ bool skinny_supported(const frisk_b200_gemm_desc& d) {
   GemmDims g = resolve_dims(d);
   if (g.K % 8 || g.lda % 8 || g.ldb % 8) return false;
   if (g.N > (int64_t)INT32_MAX / 16 || g.K > INT32_MAX / 2) return false;
+  // the K slice of X a CTA stages must fit shared memory with the deepest split there is
+  // (K <= 65536 for 16-bit operands); deeper products go to the tcgen05 kernels
+  if (make_plan(d, kNumSMsDefault).smem > kMaxSmem) return false;
   return true;
 }
 
@@ -441,7 +440,10 @@ extern "C" int frisk_b200_gemm_skinny_static(int device, const frisk_b200_gemm_d
   if (rc) return rc;
   if (!skinny_supported(*desc)) return FRISK_B200_E_UNSUPPORTED;
   if (skinny_workspace_bytes(*desc) > kStaticScratchBytes) return FRISK_B200_E_TOO_LARGE;
-  if (cudaSetDevice(device) != cudaSuccess) return FRISK_B200_E_CUDA;
+  const GemmExtents ext = gemm_extents(*desc);
+  if (ranges_overlap(C, ext.c, A, ext.a) || ranges_overlap(C, ext.c, B, ext.b)) return FRISK_B200_E_OVERLAP;
+  DeviceGuard guard(device);  // the caller's current device is put back on return
+  if (guard.error() != cudaSuccess) return FRISK_B200_E_CUDA;
   void* scratch = nullptr;
   if ((rc = static_scratch_for(device, &scratch))) return rc;
   cudaStream_t s = static_cast<cudaStream_t>(stream);

@@ -69,6 +69,27 @@ def gemm_inputs(M, N, K, dtype_ab, trans_a=False, trans_b=False, seed=0, dist="u
     return to_storage(a, dtype_ab), to_storage(b, dtype_ab)
 
 
+def gemm_inputs_streamed(M, N, K, dtype_ab, trans_a=False, trans_b=False, seed=0, dist="normal_rsqrt_k",
+                         chunk_rows=128, storage=True, **_):
+    """The same values as :func:`gemm_inputs`, yielded as ``(name, first_row, rows_in_storage_form)``
+    row blocks of the A buffer and then of the B buffer, so that a tensor too large to hold
+    twice on the host (the deep-K workload: 2 x 2 GiB) can be sent to the device piece by piece
+    while the caller keeps only the rows its sampled check needs.  Row blocks of a normal
+    draw consume the generator exactly like one large draw.  ``storage=False`` yields the scaled
+    fp32 values before the rounding to ``dtype_ab`` (for callers that round on the device)."""
+    if dist not in ("normal_rsqrt_k", "act_weight"):
+        raise ValueError("streamed inputs exist for the normal distributions only")
+    rng = np.random.default_rng(seed)
+    a_shape = (K, M) if trans_a else (M, K)
+    b_shape = (N, K) if trans_b else (K, N)
+    scales = (1.0 / math.sqrt(K),) * 2 if dist == "normal_rsqrt_k" else (1.0, 0.02)
+    for name, shape, scale in (("a", a_shape, scales[0]), ("b", b_shape, scales[1])):
+        for r0 in range(0, shape[0], chunk_rows):
+            rows = min(chunk_rows, shape[0] - r0)
+            vals = _normal(rng, (rows, shape[1]), scale)
+            yield name, r0, (to_storage(vals, dtype_ab) if storage else vals)
+
+
 def attention_inputs(B, H, S, D, dtype="bf16", seed=3, **_):
     """Q, K, V as compact BHSD arrays in storage form, N(0,1), drawn in that order."""
     rng = np.random.default_rng(seed)

@@ -15,8 +15,12 @@ def f32_to_bf16_bits(x):
     """fp32 array -> uint16 bf16 bit patterns, RNE; NaN stays NaN."""
     x = np.ascontiguousarray(x, dtype=np.float32)
     u = x.view(np.uint32)
-    bias = ((u >> 16) & 1) + np.uint32(0x7FFF)
-    r = ((u + bias) >> 16).astype(np.uint16)
+    r = u >> np.uint32(16)              # one temporary, updated in place from here on
+    r &= np.uint32(1)
+    r += np.uint32(0x7FFF)
+    r += u
+    r >>= np.uint32(16)
+    r = r.astype(np.uint16)
     nan = np.isnan(x)
     if nan.any():
         r = np.where(nan, np.uint16(0x7FC0), r)

@@ -63,6 +63,27 @@ def test_f32_config_1024(ctx):
     assert err < 1e-5  # fp32 accumulation of 1024 terms is far inside the 1e-3 budget
 
 
+def test_f32_config_1024_built_through_the_ir_builders(ctx):
+    """The same workload the way the benchmark states it: the bind_test-style kernel (8 x 8 grid of
+    128-thread blocks, 128 x 32 / 32 x 128 shared tiles, test/python/bind_test.py:28-58) built with
+    the builders over f32 memrefs, then executed, against the fp64 oracle."""
+    import torch
+
+    import frisk_b200 as F
+    from tests.test_frontend import build_bind_test_module
+    spec = inputs.WORKLOADS["gemm_f32_1024"]
+    M, N, K = spec["M"], spec["N"], spec["K"]
+    mod = build_bind_test_module(clear_accum=True, with_side_ops=False, dtype_name="f32", shape=(M, N))
+    assert mod.verify() and "frisk.gemm" in str(mod) and "memref<1024x1024xf32, 1>" in str(mod)
+    a, b = inputs.gemm_inputs(**spec)
+    ta, tb = to_device(a, "fp32"), to_device(b, "fp32")
+    tc = torch.full((M, N), float("nan"), dtype=torch.float32, device="cuda")
+    F.execute(mod, ta, tb, tc, torch.empty(M, dtype=torch.float32, device="cuda"))
+    torch.cuda.synchronize()
+    err = rel_frobenius(to_host(tc, "fp32"), gemm_oracle.gemm_fp64(a, b, "fp32"))
+    assert err <= TOL["fp32"] and err < 1e-5, err
+
+
 @pytest.mark.parametrize("ta,tb", [(False, False), (False, True), (True, False), (True, True)])
 def test_f32_transposes_ragged(ctx, ta, tb):
     check(ctx, 100, 77, 51, "fp32", "fp32", ta, tb, 11)
@@ -166,6 +187,58 @@ def test_tc_config_4096_nt(ctx):
     assert rel_frobenius(from_storage(got, "fp16"), lib) <= TOL["fp16"]
 
 
+def test_deepk_config(ctx):
+    """bf16 GEMM M = N = 8192, K = 131072 at its own size (2048 k-blocks per tile, 1024 tiles on 74 CTA
+    pairs, both tensor-memory accumulators).  The whole product is 17.6 TFLOP, out of reach for a
+    CPU, so the fp64 oracle covers a sample: 64 random rows x 64 random columns with the full K
+    extent plus two whole 256 x 256 blocks, one interior and one in the last tile row and column.
+    The whole matrix is covered by a bit-identical rerun.  Contract:
+    lib/Dialect/Frisk/IR/FriskOps.cpp:416-426, LegacyImportSemantics.cpp:26-44."""
+    import torch
+    spec = inputs.WORKLOADS["gemm_bf16_deepk"]
+    M, N, K = spec["M"], spec["N"], spec["K"]
+    rng = np.random.default_rng(6)
+    rows = np.unique(np.concatenate([rng.choice(M, 64, replace=False), np.arange(2304, 2560), np.arange(M - 256, M)]))
+    cols = np.unique(np.concatenate([rng.choice(N, 64, replace=False), np.arange(4352, 4608), np.arange(N - 256, N)]))
+    dev = {"a": torch.empty(M, K, dtype=torch.bfloat16, device="cuda"),
+           "b": torch.empty(N, K, dtype=torch.bfloat16, device="cuda")}
+    keep = {"a": np.zeros((len(rows), K), np.uint16), "b": np.zeros((len(cols), K), np.uint16)}
+    want = {"a": rows, "b": cols}
+    # 2 x 2^30 values: the bulk is rounded to bf16 on the device (round-to-nearest-even, like the
+    # host-side to_storage the sampled rows go through; the two are compared below)
+    for name, r0, blk in inputs.gemm_inputs_streamed(**spec, chunk_rows=256, storage=False):
+        dev[name][r0:r0 + blk.shape[0]].copy_(torch.from_numpy(blk).cuda().to(torch.bfloat16))
+        sel = np.nonzero((want[name] >= r0) & (want[name] < r0 + blk.shape[0]))[0]
+        keep[name][sel] = to_storage(blk[want[name][sel] - r0], "bf16")
+    for name in ("a", "b"):
+        idx = torch.from_numpy(want[name]).cuda()
+        assert np.array_equal(to_host(dev[name][idx], "bf16"), keep[name])
+    c = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+    desc = capi.gemm_desc(M, N, K, "bf16", "bf16", False, True, clear_accum=True)
+    assert capi.load().frisk_b200_gemm_select(desc) == capi.ALGO_TCGEN05_PAIR
+    stream = torch.cuda.current_stream().cuda_stream
+    ctx.gemm(desc, dev["a"].data_ptr(), dev["b"].data_ptr(), c.data_ptr(), stream=stream)
+    ctx.check(stream)
+    got = from_storage(to_host(c, "bf16"), "bf16")
+    assert np.isfinite(got).all()
+    a64 = from_storage(keep["a"], "bf16").astype(np.float64)
+    b64 = from_storage(keep["b"], "bf16").astype(np.float64)
+    ri, ci = {int(r): i for i, r in enumerate(rows)}, {int(c_): i for i, c_ in enumerate(cols)}
+
+    def sample_err(rr, cc):
+        ref = a64[[ri[int(r)] for r in rr]] @ b64[[ci[int(c_)] for c_ in cc]].T
+        return rel_frobenius(got[np.ix_(rr, cc)], ref)
+
+    errs = {"cross": sample_err(rows, cols),
+            "interior_block": sample_err(np.arange(2304, 2560), np.arange(4352, 4608)),
+            "last_block": sample_err(np.arange(M - 256, M), np.arange(N - 256, N))}
+    assert max(errs.values()) <= TOL["bf16"], errs
+    c2 = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+    ctx.gemm(desc, dev["a"].data_ptr(), dev["b"].data_ptr(), c2.data_ptr(), stream=stream)
+    ctx.check(stream)
+    assert torch.equal(c.view(torch.int16), c2.view(torch.int16))
+
+
 # ------------------------------------------------------------------ skinny
 def test_skinny_config(ctx):
     spec = inputs.WORKLOADS["gemm_bf16_skinny"]
@@ -218,6 +291,19 @@ def test_gemm_host_entry_pipelined_panels(ctx):
         ctx.gemm_host(desc, a.ctypes.data, b.ctypes.data, c.ctypes.data)
         ref = gemm_oracle.gemm_fp64(a, b, dt, False, True, c0, dt)
         assert rel_frobenius(from_storage(c, dt), ref) <= TOL[dt], (M, N, K, dt)
+
+
+def test_gemm_host_entry_short_last_panel_and_explicit_algo(ctx):
+    """M just above a panel boundary: the 16-row remainder is merged into the panel before it and
+    every panel runs the kernel chosen for the whole problem; an explicit algorithm is honoured."""
+    M, N, K = 1040, 4096, 4096
+    a, b = inputs.gemm_inputs(M, N, K, "fp16", False, True, 45, "normal_rsqrt_k")
+    ref = gemm_oracle.gemm_fp64(a, b, "fp16", False, True)
+    for algo in (capi.ALGO_AUTO, capi.ALGO_TCGEN05, capi.ALGO_TCGEN05_PAIR):
+        c = np.full((M, N), np.nan, np.float16)
+        desc = capi.gemm_desc(M, N, K, "fp16", "fp16", False, True, algo=algo)
+        ctx.gemm_host(desc, a.ctypes.data, b.ctypes.data, c.ctypes.data)
+        assert np.isfinite(c).all() and rel_frobenius(c, ref) <= TOL["fp16"], algo
 
 
 def test_contract_errors_before_launch(ctx):

@@ -58,3 +58,21 @@ def test_static_scratch_entry_refuses_oversize_and_bad_layout():
     assert "capacity" in capi.strerror(-9)
     wide = capi.gemm_desc(64, 1024, 1024, "bf16", "bf16", False, True)
     assert lib.frisk_b200_gemm_skinny_static(0, ctypes.byref(wide), 16, 16, 16, None) == -6
+
+
+def test_static_scratch_entry_refuses_aliased_output_and_keeps_the_current_device():
+    import torch
+    lib = capi.load()
+    M, N, K = 16, 1024, 1024
+    x = torch.zeros(M * K + M * N, dtype=torch.bfloat16, device="cuda")
+    w = torch.zeros(N, K, dtype=torch.bfloat16, device="cuda")
+    desc = capi.gemm_desc(M, N, K, "bf16", "bf16", False, True)
+    before = torch.cuda.current_device()
+    # the output begins inside the activations: refused like the ordinary entry refuses it
+    rc = lib.frisk_b200_gemm_skinny_static(0, ctypes.byref(desc), x.data_ptr(), w.data_ptr(), x.data_ptr() + 64, None)
+    assert rc == -4
+    rc = lib.frisk_b200_gemm_skinny_static(0, ctypes.byref(desc), x.data_ptr(), w.data_ptr(),
+                                           x.data_ptr() + M * K * 2, torch.cuda.current_stream().cuda_stream)
+    capi.raise_for(rc)
+    torch.cuda.synchronize()
+    assert torch.cuda.current_device() == before
