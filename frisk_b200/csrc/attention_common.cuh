@@ -31,6 +31,15 @@ __device__ __forceinline__ float ex2f(float x) {
   return y;
 }
 
+// The reference's exponential (benchmark/layout/execution/tiled_attention.py:511-513 emits
+// ex2.approx.f32, and its qualification forbids .ftz): subnormal inputs and results are kept.
+// Used by the normalised mode, which follows the reference's arithmetic to the letter.
+__device__ __forceinline__ float ex2f_ieee_range(float x) {
+  float y;
+  asm("ex2.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 __device__ __forceinline__ float max3f(float a, float b, float c) {
   float d;
   asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));

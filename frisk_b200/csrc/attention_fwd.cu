@@ -307,8 +307,8 @@ __global__ void __launch_bounds__(kThreads, 1)
               for (int c = 0; c < 4; ++c)
 #pragma unroll
                 for (int i = 0; i < 32; ++i)
-                  sum += ex2f(__fmul_rn(__fsub_rn(__uint_as_float(sr[c][i]), m_new), kLog2e));
-              const float carry = (m_run == -INFINITY) ? 0.f : l_run * ex2f(__fmul_rn(__fsub_rn(m_run, m_new), kLog2e));
+                  sum += ex2f_ieee_range(__fmul_rn(__fsub_rn(__uint_as_float(sr[c][i]), m_new), kLog2e));
+              const float carry = (m_run == -INFINITY) ? 0.f : l_run * ex2f_ieee_range(__fmul_rn(__fsub_rn(m_run, m_new), kLog2e));
               l_run = carry + sum;
               m_run = m_new;
             }
@@ -323,7 +323,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                 for (int e = 0; e < 2; ++e) {
                   const int col = c * 32 + 2 * i + e;
                   const float sc = __fmul_rn(__uint_as_float(sr[c][2 * i + e]), p.scale);
-                  const float ex = (col > limit) ? 0.f : ex2f(__fmul_rn(__fsub_rn(sc, m_run), kLog2e));
+                  const float ex = (col > limit) ? 0.f : ex2f_ieee_range(__fmul_rn(__fsub_rn(sc, m_run), kLog2e));
                   pv[e] = __fdiv_rn(ex, l_run);
                 }
                 pk[i] = pack16<BF16>(pv[0], pv[1]);

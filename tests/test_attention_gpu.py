@@ -221,3 +221,31 @@ def test_normalized_mode_long_sequence(ctx):
     assert np.isfinite(got).all()
     assert rel_frobenius(got, ref) <= 2e-3
     assert np.array_equal(got[0, 0, 0], from_storage(v, "bf16")[0, 0, 0])  # query 0 sees only key 0: P = 1 exactly
+
+
+def test_launch_contract_refusals(ctx):
+    """The launch validation of benchmark/layout/execution/tiled_execution.py:113-139: an output that
+    overlaps an input, or a base address that is not 16-byte aligned, is refused before anything runs."""
+    import torch
+    B, H, S, D = 1, 2, 256, 128
+    n = B * H * S * D
+    buf = torch.zeros(3 * n, dtype=torch.bfloat16, device="cuda")
+    q, k, v = (buf[i * n:(i + 1) * n] for i in range(3))
+    o = torch.zeros(n + 64, dtype=torch.bfloat16, device="cuda")
+    desc = capi.attn_desc(B, H, S, S, D, D ** -0.5, True, "bf16")
+    s = torch.cuda.current_stream().cuda_stream
+    ctx.attention_fwd(desc, q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), stream=s)  # disjoint: accepted
+    ctx.check(s)
+    for alias in (q, k, v):
+        with pytest.raises(ValueError, match="overlaps"):
+            ctx.attention_fwd(desc, q.data_ptr(), k.data_ptr(), v.data_ptr(), alias.data_ptr(), stream=s)
+    with pytest.raises(ValueError, match="overlaps"):  # partial: the output begins in Q's last 16 bytes
+        ctx.attention_fwd(desc, q.data_ptr(), k.data_ptr(), v.data_ptr(), q.data_ptr() + n * 2 - 16, stream=s)
+    for which in range(4):
+        ptrs = [q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr()]
+        ptrs[which] += 2
+        with pytest.raises(ValueError, match="16-byte"):
+            ctx.attention_fwd(desc, *ptrs, stream=s)
+    # inputs may alias each other
+    ctx.attention_fwd(desc, q.data_ptr(), q.data_ptr(), q.data_ptr(), o.data_ptr(), stream=s)
+    ctx.check(s)
