@@ -2,12 +2,15 @@
 """Benchmark of the GEMM / attention hot path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py --case tcgen05|skinny|simt|attention [--launches L]   (one kernel alone, for profilers)
 
 Prints ONE JSON line.  The headline workload is the fp16 GEMM M=N=K=4096, A row-major,
 B column-major (NT), fp32 accumulation, fp16 output, on the tcgen05 kernel.  A "step" is
 one pass of that GEMM.  With N > 1 (launched by torchrun, one rank per GPU) every rank
-runs the same per-GPU problem on its own M-row shard of a 4096*N x 4096 x 4096 product
-(independent output tiles, no collective): weak scaling.
+runs the same per-GPU problem (independent output tiles, no collective): weak scaling.
+The strong-scaled forms of every workload that shards (one 4096^3 product cut into M/N
+blocks, the skinny GEMM cut along N, the attention cut along batch x head, the deep-K GEMM
+cut along K with its one exchange step) are timed AND checked in `secondary`.
 
 Timing: CUDA events on the launching stream around every step, W >= 3 warm-up steps,
 inputs rotate through buffer sets larger than L2 so no step finds its operands cached,
@@ -16,7 +19,8 @@ barrier + synchronize on both sides of the timed region, max over ranks.
 Keys beyond the basic contract: `e2e` (same GEMM through the host-buffer C-ABI entry
 point, pinned host memory, copies inside the timed region), `roofline`, `cpu_baseline`
 (the numpy oracle on the host cores), `clocks`, `gpu_launches`, and `secondary` (the other
-benchmark workloads, kernel-only, for information).
+benchmark workloads, kernel-only; every entry carries `err`, the relative Frobenius error of
+a sample of its output against the fp64 CPU oracle, taken outside the timed region).
 """
 import argparse
 import json
@@ -31,10 +35,12 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 METRIC = "TFLOP/s (% of B200 dense peak) for GEMM & attention at 1/2/4/8 GPUs"
+WORKLOAD = "fp16 GEMM M=N=K=4096, A row-major, B column-major (NT), fp32 accumulate, fp16 out"
 NOMINAL_TENSOR_TFLOPS = 2250.0
 NOMINAL_HBM_GBS = 8000.0
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 L2_BYTES = 126 * 1024 * 1024
+TOL_GEMM16, TOL_ATTN = 5e-3, 1e-2
 
 
 def measured_peaks():
@@ -101,14 +107,12 @@ class ClockSampler:
                 pass
             time.sleep(0.002)
 
-    def stop(self, t0, t1):
-        self.stop_flag = True
-        if self.nvml is None:
-            return self._smi_once()
-        if self.thread is not None:
-            self.thread.join(timeout=1)
+    def window(self, t0, t1):
+        """Summary of the samples taken between two wall-clock instants (sampling goes on)."""
         n = self.nvml
-        rows = [s for s in self.samples if t0 <= s[0] <= t1] or self.samples[-3:]
+        if n is None:
+            return self._smi_once()
+        rows = [s for s in list(self.samples) if t0 <= s[0] <= t1] or list(self.samples)[-3:]
         if not rows:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
         sm = sorted(r[1] for r in rows)
@@ -122,9 +126,21 @@ class ClockSampler:
             mx = n.nvmlDeviceGetMaxClockInfo(self.handle, n.NVML_CLOCK_SM)
         except Exception:
             mx = None
+        hist = {}
+        for v in sm:
+            hist[int(v)] = hist.get(int(v), 0) + 1
         return {"sm_mhz": float(sm[len(sm) // 2]), "sm_min_mhz": float(sm[0]), "sm_max_mhz": float(mx) if mx else None,
                 "reasons": reasons, "samples": len(rows), "power_w_max": round(max(r[3] for r in rows), 1),
+                "sm_mhz_histogram": {str(k): hist[k] for k in sorted(hist)},
                 "source": "nvml, 2 ms polling inside the timed region"}
+
+    def stop(self, t0, t1):
+        out = self.window(t0, t1)
+        self.stop_flag = True
+        if self.thread is not None:
+            self.thread.join(timeout=1)
+        out.pop("sm_mhz_histogram", None)
+        return out
 
     def _smi_once(self):
         try:
@@ -172,19 +188,54 @@ def time_steps(fn, steps, warmup, torch, dist, world):
     return total, per, (t_wall0, t_wall1)
 
 
-def gemm_sets(torch, M, N, K, dtype, trans_b, scale_a, scale_b, out_dtype=None, min_bytes=2.5 * L2_BYTES):
+def device_normal(torch, shape, dtype, scale, seed):
+    """Seeded N(0,1)*scale drawn on the device (used for the large secondary workloads, whose
+    2 x 10^9 values would take minutes from a host generator)."""
+    g = torch.Generator(device="cuda")
+    g.manual_seed(seed)
+    x = torch.randn(shape, device="cuda", dtype=torch.float32, generator=g)
+    if scale != 1.0:
+        x *= scale
+    return x.to(dtype)
+
+
+def gemm_sets(torch, M, N, K, dtype, trans_b, scale_a, scale_b, out_dtype=None, min_bytes=2.5 * L2_BYTES, seed=100):
     """Enough (A, B, C) sets that a rotation through them exceeds L2 several times over."""
     item = torch.finfo(dtype).bits // 8
     per_set = (M * K + N * K + M * N) * item
     n = max(2, int(math.ceil(min_bytes / per_set)))
     n = min(n, 8)
     sets = []
-    for _ in range(n):
-        a = (torch.randn(M, K, device="cuda", dtype=torch.float32) * scale_a).to(dtype)
-        b = (torch.randn((N, K) if trans_b else (K, N), device="cuda", dtype=torch.float32) * scale_b).to(dtype)
+    for i in range(n):
+        a = device_normal(torch, (M, K), dtype, scale_a, seed + 2 * i)
+        b = device_normal(torch, (N, K) if trans_b else (K, N), dtype, scale_b, seed + 2 * i + 1)
         c = torch.empty(M, N, device="cuda", dtype=out_dtype or dtype)
         sets.append((a, b, c))
     return sets
+
+
+def rel_err_gemm_sample(torch, a, b, c, rows, cols, c_col0=0):
+    """Checker, outside every timed region: relative Frobenius error of C[rows, cols] against the
+    fp64 CPU oracle over the same device inputs (A [M,K], B [N,K], both K-contiguous).  `a` / `b`
+    may be lists of K-slices (the split-K ranks' shards gathered by the caller)."""
+    import numpy as np
+
+    from oracle.numerics import rel_frobenius
+    ri = torch.as_tensor(rows, device=c.device)
+    ci = torch.as_tensor(cols, device=c.device)
+    a_parts = a if isinstance(a, (list, tuple)) else [a]
+    b_parts = b if isinstance(b, (list, tuple)) else [b]
+    ref = np.zeros((len(rows), len(cols)))
+    for ap, bp in zip(a_parts, b_parts):
+        ref += ap[ri].double().cpu().numpy() @ bp[ci].double().cpu().numpy().T
+    got = c[ri][:, ci - c_col0].double().cpu().numpy()
+    return rel_frobenius(got, ref)
+
+
+def sample_indices(n, count, seed):
+    import numpy as np
+    rng = np.random.default_rng(seed)
+    return np.sort(rng.choice(n, min(count, n), replace=False))
 
 
 # ----------------------------------------------------------------------------- our arm
@@ -204,8 +255,15 @@ def run_ours(args):
     stream = torch.cuda.current_stream().cuda_stream
     peaks, peak_kind = measured_peaks()
 
+    # ---- headline inputs: set 0 is the seeded workload of the specification (numpy PCG64, seed 1,
+    # N(0,1)/sqrt(K) for both operands); the further sets only exist to defeat L2
+    from oracle import inputs as seeded
     M = N = K = 4096
-    sets = gemm_sets(torch, M, N, K, torch.float16, True, 1.0 / math.sqrt(K), 1.0)
+    spec = seeded.WORKLOADS["gemm_f16_4096_nt"]
+    a0, b0 = seeded.gemm_inputs(**spec)
+    sets = [(torch.from_numpy(a0).cuda(), torch.from_numpy(b0).cuda(),
+             torch.empty(M, N, device="cuda", dtype=torch.float16))]
+    sets += gemm_sets(torch, M, N, K, torch.float16, True, 1.0 / math.sqrt(K), 1.0 / math.sqrt(K), min_bytes=2 * L2_BYTES)
     desc = capi.gemm_desc(M, N, K, "fp16", "fp16", False, True, clear_accum=True)
     flop = 2.0 * M * N * K
 
@@ -219,15 +277,24 @@ def run_ours(args):
         time.sleep(0.3)
     total_ms, per, wall = time_steps(step, args.steps, args.warmup, torch, dist, world)
     ctx.check(stream)
-    clocks = sampler.stop(*wall) if rank == 0 else None
+    clocks = sampler.window(*wall) if rank == 0 else None
+    if clocks:
+        clocks.pop("sm_mhz_histogram", None)
     ms_per_step = total_ms / args.steps
     value = world * flop * args.steps / (total_ms * 1e-3) / 1e12
     kernel_ms = sum(per) / len(per)
     achieved = flop / (kernel_ms * 1e-3) / 1e12
+    # the seeded set's result: checksum of the whole C and a sampled check against the fp64 oracle
+    step(0)
+    torch.cuda.synchronize()
+    c_seeded = sets[0][2]
+    headline_err = rel_err_gemm_sample(torch, sets[0][0], sets[0][1], c_seeded, sample_indices(M, 64, 5),
+                                       sample_indices(N, 256, 6))
+    headline_checksum = float(c_seeded.double().abs().sum().item())
 
     # ---- end to end through the host-buffer C-ABI entry (pinned host memory)
-    ha = (torch.randn(M, K) / math.sqrt(K)).to(torch.float16).pin_memory()
-    hb = torch.randn(N, K).to(torch.float16).pin_memory()
+    ha = torch.from_numpy(a0).pin_memory()
+    hb = torch.from_numpy(b0).pin_memory()
     hc = torch.empty(M, N, dtype=torch.float16).pin_memory()
     e2e_steps = max(1, min(args.steps, 10))
     for _ in range(2):
@@ -245,12 +312,13 @@ def run_ours(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_s = float(t.item())
     e2e_value = world * flop * e2e_steps / e2e_s / 1e12
-    checksum = float(hc[:8, :8].float().abs().sum())
+    e2e_same_bits = bool(torch.equal(hc.view(torch.int16), c_seeded.cpu().view(torch.int16)))
+    link = host_link_rates(torch, dist, world, ha, hc)
 
     splitk_res = sharded_res = None
     if world > 1 and not args.no_secondary:
         # the short sharded workloads first: the deep-K products that follow leave the GPUs power-capped
-        sharded_res = sharded_secondary(ctx, torch, dist, world, stream, peaks)
+        sharded_res = sharded_secondary(ctx, torch, dist, world, rank, stream, peaks, a0, b0)
         splitk_res = splitk_secondary(ctx, torch, dist, world, rank, peaks)
 
     out = None
@@ -260,17 +328,22 @@ def run_ours(args):
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_per_step, 5),
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp16",
             "data": "synthetic",
-            "config": {"workload": "fp16 GEMM M=N=K=4096 per GPU, A row-major, B column-major (NT), "
-                                   "fp32 accumulate, fp16 out",
-                       "sharding": "independent M-row shards, one 4096x4096x4096 product per GPU, no collective",
+            "config": {"workload": WORKLOAD,
+                       "sharding": "weak: one whole 4096x4096x4096 product per GPU, no collective "
+                                   "(the strong split of ONE product is secondary.gemm_f16_4096_sharded)",
                        "kernel": "gemm_tcgen05_2cta (tcgen05.mma cta_group::2 256x256x16 per CTA pair, TMEM accumulators, TMA 6-stage ring, no multicast)",
+                       "inputs": "set 0: numpy PCG64 seed 1, N(0,1)/sqrt(K); sets 1.. : seeded device draws",
                        "l2": f"inputs rotate through {len(sets)} operand sets "
                              f"({len(sets) * 3 * M * N * 2 / 2**20:.0f} MiB > 126 MiB L2)",
                        "pct_of_nominal_dense_peak": round(100 * value / world / NOMINAL_TENSOR_TFLOPS, 2)},
             "e2e": {"value": round(e2e_value, 3), "unit": "TFLOP/s", "h2d_bytes_per_step": 2 * M * K * 2,
-                    "d2h_bytes_per_step": M * N * 2, "steps": e2e_steps, "checksum": checksum},
+                    "d2h_bytes_per_step": M * N * 2, "steps": e2e_steps,
+                    "same_bits_as_device_path": e2e_same_bits, "host_link": link},
             "gpu_launches": args.steps,
             "clocks": clocks,
+            "checked": {"err": float(f"{headline_err:.3e}"), "tolerance": TOL_GEMM16, "ok": headline_err <= TOL_GEMM16,
+                        "sample": "64 rows x 256 columns of the seeded set against the fp64 CPU oracle",
+                        "checksum_abs_sum": headline_checksum},
             "roofline": {"bound": "tensor", "achieved": round(achieved, 2), "peak": peaks["bf16_tflops"],
                          "unit": "TFLOP/s", "frac": round(achieved / peaks["bf16_tflops"], 4),
                          "traffic": ncu_traffic("gemm_tcgen05_f16_4096"), "peak_source": peak_kind + " (burst)",
@@ -279,11 +352,13 @@ def run_ours(args):
         if world == 1:
             out["cpu_baseline"] = cpu_baseline_gemm(M, N, K)
             if not args.no_secondary:
-                out["secondary"] = secondary(ctx, torch, stream, peaks, args)
+                out["secondary"] = secondary(ctx, torch, stream, peaks, args, sampler, sets, desc)
         if splitk_res is not None:
             out["secondary"] = {"gemm_bf16_deepk_splitk": splitk_res}
             out["secondary"].update(sharded_res or {})
         print(json.dumps(out), flush=True)
+    if rank == 0:
+        sampler.stop(0, 0)
     ctx.close()
     if world > 1:
         dist.barrier()
@@ -291,70 +366,211 @@ def run_ours(args):
     return out
 
 
-def sharded_secondary(ctx, torch, dist, world, stream, peaks):
-    """The two workloads that shard without communication, strong-scaled over the ranks: the skinny GEMM
-    with N/g columns of W per GPU (X replicated) and the causal attention with 256/g (batch, head) pairs
-    per GPU.  Time = max over ranks; throughput = the whole workload over that time."""
+def host_link_rates(torch, dist, world, pinned_in, pinned_out):
+    """What bounds the end-to-end figure: the rates this rank's pinned buffers reach over the host
+    link in each direction, one direction at a time (CUDA events), the slowest rank reported."""
+    try:
+        dev_in = torch.empty_like(pinned_in, device="cuda")
+        dev_out = torch.empty_like(pinned_out, device="cuda")
+        res = {}
+        for name, dst, src in (("h2d_gbs", dev_in, pinned_in), ("d2h_gbs", pinned_out, dev_out)):
+            dst.copy_(src, non_blocking=True)
+            torch.cuda.synchronize()
+            if world > 1:
+                dist.barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(4):
+                dst.copy_(src, non_blocking=True)
+            e1.record()
+            torch.cuda.synchronize()
+            gbs = 4 * src.numel() * src.element_size() / (e0.elapsed_time(e1) * 1e-3) / 1e9
+            if world > 1:
+                t = torch.tensor([gbs], dtype=torch.float64, device="cuda")
+                dist.all_reduce(t, op=dist.ReduceOp.MIN)
+                gbs = float(t.item())
+            res[name] = round(gbs, 1)
+        try:
+            res["cpu_affinity"] = len(os.sched_getaffinity(0))
+        except Exception:
+            pass
+        res["note"] = "slowest rank; all ranks copy at the same time and share the host's memory and root complexes"
+        return res
+    except Exception as e:  # noqa: BLE001
+        return {"error": str(e)}
+
+
+def block_grid(world):
+    """How ONE 4096^3 product is cut across the GPUs: 2 -> M/2; 4 -> 2 x 2; 8 -> 4 x 2 (M x N)."""
+    return {1: (1, 1), 2: (2, 1), 4: (2, 2), 8: (4, 2)}.get(world, (world, 1))
+
+
+def sharded_secondary(ctx, torch, dist, world, rank, stream, peaks, a_full, b_full):
+    """The workloads that shard without communication, strong-scaled over the ranks: ONE fp16 4096^3
+    product cut into M x N blocks, the skinny GEMM with N/g columns of W per GPU (X replicated), the
+    causal attention with 256/g (batch, head) pairs per GPU.  Time = max over ranks; throughput = the
+    whole workload over that time.  Every rank checks a sample of its own shard against the fp64 CPU
+    oracle outside the timed region; `err` is the largest error over the ranks."""
     from frisk_b200 import capi
     res = {}
+
+    def worst(err):
+        t = torch.tensor([err], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    try:
+        M = N = K = 4096
+        gm, gn = block_grid(world)
+        bm, bn = M // gm, N // gn
+        i, j = divmod(rank, gn)
+        # shards are slices of the full seeded host tensors: A rows and B rows (= C columns) of this block
+        a = torch.from_numpy(a_full[i * bm:(i + 1) * bm]).cuda()
+        b = torch.from_numpy(b_full[j * bn:(j + 1) * bn]).cuda()
+        n_sets = max(2, min(8, int(math.ceil(2.5 * L2_BYTES / ((bm * K + bn * K + bm * bn) * 2)))))
+        sets = [(a, b, torch.empty(bm, bn, device="cuda", dtype=torch.float16))]
+        sets += [(a.clone(), b.clone(), torch.empty(bm, bn, device="cuda", dtype=torch.float16)) for _ in range(n_sets - 1)]
+        desc = capi.gemm_desc(bm, bn, K, "fp16", "fp16", False, True)
+        total, _, _ = time_steps(lambda s: ctx.gemm(desc, *(t.data_ptr() for t in sets[s % len(sets)]), stream=stream),
+                                 20, 3, torch, dist, world)
+        ctx.check(stream)
+        ms = total / 20
+        err = worst(rel_err_gemm_sample(torch, a, b, sets[0][2], sample_indices(bm, 64, 7 + rank),
+                                        sample_indices(bn, 256, 8 + rank)))
+        tf = 2.0 * M * N * K / ms / 1e9
+        res["gemm_f16_4096_sharded"] = {"ms": round(ms, 5), "tflops": round(tf, 2), "n_gpus": world, "scaling": "strong",
+                                        "blocks": f"{gm} x {gn} blocks of {bm} x {bn}",
+                                        "per_gpu_frac_of_nominal": round(tf / world / NOMINAL_TENSOR_TFLOPS, 4),
+                                        "err": float(f"{err:.3e}"), "checked": err <= TOL_GEMM16}
+        del sets, a, b
+    except Exception as e:  # noqa: BLE001
+        res["gemm_f16_4096_sharded"] = {"error": str(e)}
     try:
         M, N, K = 16, 28672, 8192
         n_local = N // world
-        sets = gemm_sets(torch, M, n_local, K, torch.bfloat16, True, 1.0, 0.02, min_bytes=2.5 * L2_BYTES)
+        x = device_normal(torch, (M, K), torch.bfloat16, 1.0, 2)             # replicated activations
+        sets = []
+        n_sets = max(2, min(8, int(math.ceil(2.5 * L2_BYTES / (n_local * K * 2)))))
+        for s in range(n_sets):
+            w = device_normal(torch, (n_local, K), torch.bfloat16, 0.02, 1000 + 97 * rank + s)
+            sets.append((x, w, torch.empty(M, n_local, device="cuda", dtype=torch.bfloat16)))
         desc = capi.gemm_desc(M, n_local, K, "bf16", "bf16", False, True)
-        total, _, _ = time_steps(lambda i: ctx.gemm(desc, *(t.data_ptr() for t in sets[i % len(sets)]), stream=stream),
-                                 10, 3, torch, dist, world)
-        ms = total / 10
+        total, _, _ = time_steps(lambda s: ctx.gemm(desc, *(t.data_ptr() for t in sets[s % len(sets)]), stream=stream),
+                                 20, 3, torch, dist, world)
+        ctx.check(stream)
+        ms = total / 20
+        ctx.gemm(desc, *(t.data_ptr() for t in sets[0]), stream=stream)
+        torch.cuda.synchronize()
+        err = worst(rel_err_gemm_sample(torch, x, sets[0][1], sets[0][2], list(range(M)), sample_indices(n_local, 512, 9 + rank)))
         byts = (N * K + world * M * K + M * N) * 2
         res["gemm_bf16_skinny_sharded"] = {"ms": round(ms, 5), "gbs": round(byts / ms / 1e6, 1), "n_gpus": world,
-                                           "columns_per_gpu": n_local,
-                                           "per_gpu_frac_of_measured_hbm": round(byts / ms / 1e6 / world / peaks["hbm_gbs"], 4)}
+                                           "scaling": "strong", "columns_per_gpu": n_local,
+                                           "per_gpu_frac_of_measured_hbm": round(byts / ms / 1e6 / world / peaks["hbm_gbs"], 4),
+                                           "err": float(f"{err:.3e}"), "checked": err <= TOL_GEMM16}
         del sets
     except Exception as e:  # noqa: BLE001
         res["gemm_bf16_skinny_sharded"] = {"error": str(e)}
     try:
         B, H, S, D = 8, 32, 4096, 128
         heads = B * H // world
-        q, k, v = (torch.randn(1, heads, S, D, device="cuda", dtype=torch.bfloat16) for _ in range(3))
+        q, k, v = (device_normal(torch, (1, heads, S, D), torch.bfloat16, 1.0, 3000 + 3 * rank + t) for t in range(3))
         o = torch.empty_like(q)
         desc = capi.attn_desc(1, heads, S, S, D, 1.0 / math.sqrt(D), True, "bf16", "bf16")
         total, _, _ = time_steps(lambda i: ctx.attention_fwd(desc, q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),
                                                              stream=stream), 5, 3, torch, dist, world)
+        ctx.check(stream)
         ms = total / 5
+        err = worst(attention_err(torch, q, k, v, o, [0, heads - 1], D))
         fl = 4.0 * B * H * S * S * D / 2
         res["attn_bf16_causal_sharded"] = {"ms": round(ms, 5), "tflops": round(fl / ms / 1e9, 2), "n_gpus": world,
-                                           "heads_per_gpu": heads,
-                                           "per_gpu_frac_of_nominal": round(fl / ms / 1e9 / world / NOMINAL_TENSOR_TFLOPS, 4)}
+                                           "scaling": "strong", "heads_per_gpu": heads,
+                                           "per_gpu_frac_of_nominal": round(fl / ms / 1e9 / world / NOMINAL_TENSOR_TFLOPS, 4),
+                                           "err": float(f"{err:.3e}"), "checked": err <= TOL_ATTN}
     except Exception as e:  # noqa: BLE001
         res["attn_bf16_causal_sharded"] = {"error": str(e)}
     return res
 
 
+def attention_err(torch, q, k, v, o, heads, D, rows_per_head=192):
+    """Checker: sampled query rows of the given heads (flat index into dim 1) against the fp64 oracle
+    (P rounded to bf16 before P.V, causal)."""
+    import numpy as np
+
+    from oracle import attention_oracle as ao
+    from oracle.numerics import rel_frobenius
+    S = q.shape[2]
+    worst = 0.0
+    for h in heads:
+        rows = np.unique(np.concatenate([[0, 1, 127, 128, S - 1], sample_indices(S, rows_per_head, 11 + h)]))
+        qh, kh, vh = (t[0, h].float().cpu().numpy() for t in (q, k, v))
+        ref = ao.attention_head(qh, kh, vh, 1.0 / math.sqrt(D), causal=True, mode="fp64", p_dtype="bf16", rows=rows)
+        got = o[0, h].float().cpu().numpy()[rows]
+        worst = max(worst, rel_frobenius(got, ref))
+    return worst
+
+
 def splitk_secondary(ctx, torch, dist, world, rank, peaks):
     """bf16 GEMM M=N=8192, K=131072 with K split across the ranks, two ways: (fused) the tcgen05
     epilogue stores each fp32 tile into its slot in the row owner's memory over NVLink; (nccl) fp32 partials,
-    NCCL reduce-scatter pipelined over row panels, local rounding to bf16."""
+    NCCL reduce-scatter pipelined over row panels, local rounding to bf16.  After the timed region every
+    rank checks a sample of the rows it owns against the fp64 oracle over the full K (the K slices of the
+    sampled rows and columns are gathered from all ranks)."""
     from frisk_b200 import splitk
     M, N, K = 8192, 8192, 131072
-    res = {"n_gpus": world}
+    res = {"n_gpus": world, "scaling": "strong"}
 
-    def line(ms, exchange):
+    def line(ms, exchange, err):
         tf = 2.0 * M * N * K / ms / 1e9
         return {"ms": round(ms, 4), "tflops": round(tf, 2),
                 "per_gpu_frac_of_measured_sustained": round(tf / world / peaks["bf16_tflops_sustained"], 4),
-                "exchange": exchange}
+                "exchange": exchange, "err": float(f"{err:.3e}"), "checked": err <= TOL_GEMM16}
     sent = (world - 1) / world * M * N * 4 / 1e6
     try:
         k_local = K // world
-        a = torch.randn(M, k_local, device="cuda", dtype=torch.bfloat16) * (1 / math.sqrt(K))
-        b = torch.randn(N, k_local, device="cuda", dtype=torch.bfloat16)
+        a = device_normal(torch, (M, k_local), torch.bfloat16, 1 / math.sqrt(K), 4000 + rank)
+        b = device_normal(torch, (N, k_local), torch.bfloat16, 1 / math.sqrt(K), 5000 + rank)
     except Exception as e:  # noqa: BLE001
         return {"error": str(e)}
+
+    cols = sample_indices(N, 128, 21)
+    ci = torch.as_tensor(cols, device="cuda")
+    b_cols = [torch.empty(len(cols), k_local, dtype=torch.bfloat16, device="cuda") for _ in range(world)]
+    dist.all_gather(b_cols, b[ci].contiguous())
+
+    def check_owned(out_rows, row_ids):
+        """out_rows: this rank's final rows, row_ids: their global indices (same order)."""
+        import numpy as np
+        pick = sample_indices(len(row_ids), 32, 22 + rank)
+        # every rank contributes its K slice of every rank's sampled rows
+        want = torch.as_tensor(np.asarray(row_ids)[pick], device="cuda")
+        all_want = [torch.empty_like(want) for _ in range(world)]
+        dist.all_gather(all_want, want)
+        mine = []
+        for r in range(world):
+            rows_r = a[all_want[r]].contiguous()          # this rank's K slice of rank r's sampled rows
+            gathered = [torch.empty_like(rows_r) for _ in range(world)] if r == rank else None
+            dist.gather(rows_r, gathered, dst=r)
+            if r == rank:
+                mine = gathered
+        ref = np.zeros((len(pick), len(cols)))
+        for s in range(world):
+            ref += mine[s].double().cpu().numpy() @ b_cols[s].double().cpu().numpy().T
+        from oracle.numerics import rel_frobenius
+        got = out_rows[torch.as_tensor(pick, device="cuda")][:, ci].double().cpu().numpy()
+        err = rel_frobenius(got, ref)
+        t = torch.tensor([err], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
     try:
         op = splitk.SplitKGemmPush(M, N, K, world, rank, "bf16", ctx, dist.group.WORLD)
         total, per, _ = time_steps(lambda i: op.run(a, b), 5, 3, torch, dist, world)
         ctx.check(torch.cuda.current_stream().cuda_stream)
-        res["fused_push"] = line(total / 5, "epilogue 16-byte stores into this rank's slot in the owners' memory, slots summed in rank order, %.1f MB sent per GPU" % sent)
+        out = op.run(a, b)
+        torch.cuda.synchronize()
+        err = check_owned(out, list(range(rank * op.rows, (rank + 1) * op.rows)))
+        res["fused_push"] = line(total / 5, "epilogue 16-byte stores into this rank's slot in the owners' memory, slots "
+                                 "summed in rank order, %.1f MB sent per GPU" % sent, err)
         dist.barrier()
         op.close()
     except Exception as e:  # noqa: BLE001
@@ -363,74 +579,132 @@ def splitk_secondary(ctx, torch, dist, world, rank, peaks):
         plan = splitk.make_plan(M, N, K, world, rank, panels=4)
         op = splitk.SplitKGemm(plan, "bf16", ctx=ctx, group=dist.group.WORLD)
         total, per, _ = time_steps(lambda i: op.run(a, b), 5, 3, torch, dist, world)
+        out = op.run(a, b)
+        torch.cuda.synchronize()
+        row_ids = [r for lo, hi in splitk.owned_rows(plan) for r in range(lo, hi)]
+        err = check_owned(out.reshape(-1, N), row_ids)
         res["nccl"] = line(total / 5, "NCCL reduce_scatter of fp32 partials over %d row panels, %.1f MB sent per GPU"
-                           % (plan.panels, sent))
+                           % (plan.panels, sent), err)
     except Exception as e:  # noqa: BLE001
         res["nccl"] = {"error": str(e)}
     return res
 
 
-def secondary(ctx, torch, stream, peaks, args):
-    """The other benchmark workloads, kernel-only, a few steps each."""
+def secondary(ctx, torch, stream, peaks, args, sampler, headline_sets, headline_desc):
+    """The other benchmark workloads on one GPU, kernel-only, a few steps each, each checked against the
+    fp64 oracle on a sample outside its timed region."""
     from frisk_b200 import capi
     res = {}
     steps, warm = max(3, min(args.steps, 10)), 3
 
-    def timed(fn):
-        total, per, _ = time_steps(fn, steps, warm, torch, None, 1)
+    def timed(fn, n=None):
+        total, per, _ = time_steps(fn, n or steps, warm, torch, None, 1)
         ctx.check(stream)
-        return total / steps
+        return total / (n or steps)
 
-    # fp32 GEMM 1024^3 (12 MiB of operands: rotate 32 sets to stay ahead of L2)
+    # fp32 GEMM 1024^3 (12 MiB of operands: rotate enough sets to stay ahead of L2)
     try:
         M = 1024
-        sets = gemm_sets(torch, M, M, M, torch.float32, False, 1.0, 1.0, min_bytes=3 * L2_BYTES)
-        sets = sets + gemm_sets(torch, M, M, M, torch.float32, False, 1.0, 1.0, min_bytes=3 * L2_BYTES)
+        g = torch.Generator(device="cuda")
+        g.manual_seed(0)
+        sets = []
+        for _ in range(32):
+            a, b = (torch.rand(M, M, device="cuda", generator=g) * 2 - 1 for _ in range(2))
+            sets.append((a, b, torch.empty(M, M, device="cuda")))
         desc = capi.gemm_desc(M, M, M, "fp32", "fp32")
-        ms = timed(lambda i: ctx.gemm(desc, *(t.data_ptr() for t in sets[i % len(sets)]), stream=stream))
-        res["gemm_f32_1024"] = {"ms": round(ms, 5), "tflops": round(2.0 * M ** 3 / ms / 1e9, 2)}
+        ms = timed(lambda i: ctx.gemm(desc, *(t.data_ptr() for t in sets[i % len(sets)]), stream=stream), 20)
+        a, b, c = sets[0]
+        ctx.gemm(desc, a.data_ptr(), b.data_ptr(), c.data_ptr(), stream=stream)
+        torch.cuda.synchronize()
+        from oracle.numerics import rel_frobenius
+        err = rel_frobenius(c.double().cpu().numpy(), a.double().cpu().numpy() @ b.double().cpu().numpy())
+        res["gemm_f32_1024"] = {"ms": round(ms, 5), "tflops": round(2.0 * M ** 3 / ms / 1e9, 2),
+                                "frac_of_nominal_fp32_simt": round(2.0 * M ** 3 / ms / 1e9 / 80.0, 4),
+                                "err": float(f"{err:.3e}"), "checked": err <= 1e-3}
+        del sets
     except Exception as e:  # noqa: BLE001
         res["gemm_f32_1024"] = {"error": str(e)}
     # skinny bf16 16 x 28672 x 8192 (470 MB of weights: larger than L2 by itself)
     try:
         M, N, K = 16, 28672, 8192
-        sets = gemm_sets(torch, M, N, K, torch.bfloat16, True, 1.0, 0.02, min_bytes=1)
+        sets = gemm_sets(torch, M, N, K, torch.bfloat16, True, 1.0, 0.02, min_bytes=1, seed=2)
         desc = capi.gemm_desc(M, N, K, "bf16", "bf16", False, True)
-        ms = timed(lambda i: ctx.gemm(desc, *(t.data_ptr() for t in sets[i % len(sets)]), stream=stream))
+        ms = timed(lambda i: ctx.gemm(desc, *(t.data_ptr() for t in sets[i % len(sets)]), stream=stream), 20)
+        a, b, c = sets[0]
+        ctx.gemm(desc, a.data_ptr(), b.data_ptr(), c.data_ptr(), stream=stream)
+        torch.cuda.synchronize()
+        err = rel_err_gemm_sample(torch, a, b, c, list(range(M)), sample_indices(N, 1024, 12))
         byts = (N * K + M * K + M * N) * 2
         res["gemm_bf16_skinny"] = {"ms": round(ms, 5), "gbs": round(byts / ms / 1e6, 1),
                                    "frac_of_measured_hbm": round(byts / ms / 1e6 / peaks["hbm_gbs"], 4),
-                                   "frac_of_nominal_hbm": round(byts / ms / 1e6 / NOMINAL_HBM_GBS, 4)}
+                                   "frac_of_nominal_hbm": round(byts / ms / 1e6 / NOMINAL_HBM_GBS, 4),
+                                   "err": float(f"{err:.3e}"), "checked": err <= TOL_GEMM16}
+        del sets
     except Exception as e:  # noqa: BLE001
         res["gemm_bf16_skinny"] = {"error": str(e)}
     # causal attention B=8 H=32 S=4096 D=128 bf16
     try:
         B, H, S, D = 8, 32, 4096, 128
-        q, k, v = (torch.randn(B, H, S, D, device="cuda", dtype=torch.bfloat16) for _ in range(3))
+        q, k, v = (device_normal(torch, (1, B * H, S, D), torch.bfloat16, 1.0, 3 + t) for t in range(3))
         o = torch.empty_like(q)
         desc = capi.attn_desc(B, H, S, S, D, 1.0 / math.sqrt(D), True, "bf16", "bf16")
         ms = timed(lambda i: ctx.attention_fwd(desc, q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),
                                                stream=stream))
+        err = attention_err(torch, q, k, v, o, [0, 77, B * H - 1], D)
         fl = 4.0 * B * H * S * S * D / 2
         res["attn_bf16_causal"] = {"ms": round(ms, 5), "tflops": round(fl / ms / 1e9, 2),
-                                   "frac_of_nominal": round(fl / ms / 1e9 / NOMINAL_TENSOR_TFLOPS, 4)}
+                                   "frac_of_nominal": round(fl / ms / 1e9 / NOMINAL_TENSOR_TFLOPS, 4),
+                                   "err": float(f"{err:.3e}"), "checked": err <= TOL_ATTN}
         del q, k, v, o
     except Exception as e:  # noqa: BLE001
         res["attn_bf16_causal"] = {"error": str(e)}
+    # the headline GEMM in the sustained regime: back-to-back launches for more than a second, so that the
+    # power cap, not the boost clock, sets the SM frequency (the regime a long job runs in)
+    try:
+        a, b, c = headline_sets[0]
+        n_launch, flop = 12000, 2.0 * 4096 ** 3
+        for _ in range(200):
+            ctx.gemm(headline_desc, a.data_ptr(), b.data_ptr(), c.data_ptr(), stream=stream)
+        torch.cuda.synchronize()
+        t_w0 = time.time()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(n_launch):
+            s = headline_sets[i % len(headline_sets)]
+            ctx.gemm(headline_desc, s[0].data_ptr(), s[1].data_ptr(), s[2].data_ptr(), stream=stream)
+        e1.record()
+        torch.cuda.synchronize()
+        t_w1 = time.time()
+        ctx.check(stream)
+        ms = e0.elapsed_time(e1) / n_launch
+        ck = sampler.window(t_w0, t_w1)
+        tf = flop / ms / 1e9
+        res["gemm_f16_4096_sustained"] = {
+            "ms": round(ms, 5), "tflops": round(tf, 2), "seconds": round(t_w1 - t_w0, 2), "launches": n_launch,
+            "frac_of_measured_sustained": round(tf / peaks["bf16_tflops_sustained"], 4),
+            "frac_of_nominal": round(tf / NOMINAL_TENSOR_TFLOPS, 4),
+            "sm_mhz_median": ck.get("sm_mhz"), "sm_mhz_histogram": ck.get("sm_mhz_histogram"),
+            "power_w_max": ck.get("power_w_max"), "reasons": ck.get("reasons"),
+            "us_times_mhz": round(ms * 1e3 * ck["sm_mhz"], 1) if ck.get("sm_mhz") else None}
+    except Exception as e:  # noqa: BLE001
+        res["gemm_f16_4096_sustained"] = {"error": str(e)}
     # deep-K bf16 8192 x 8192 x 131072 (single GPU: whole K)
     try:
         M, N, K = 8192, 8192, 131072
-        a = (torch.randn(M, K, device="cuda", dtype=torch.bfloat16) * (1 / math.sqrt(K)))
-        b = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
+        a = device_normal(torch, (M, K), torch.bfloat16, 1 / math.sqrt(K), 4)
+        b = device_normal(torch, (N, K), torch.bfloat16, 1 / math.sqrt(K), 5)
         c = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
         desc = capi.gemm_desc(M, N, K, "bf16", "bf16", False, True)
         total, per, _ = time_steps(lambda i: ctx.gemm(desc, a.data_ptr(), b.data_ptr(), c.data_ptr(), stream=stream),
                                    3, 1, torch, None, 1)
         ctx.check(stream)
         ms = total / 3
+        err = rel_err_gemm_sample(torch, a, b, c, sample_indices(M, 48, 13), sample_indices(N, 128, 14))
         res["gemm_bf16_deepk"] = {"ms": round(ms, 4), "tflops": round(2.0 * M * N * K / ms / 1e9, 2),
                                   "frac_of_measured_sustained": round(2.0 * M * N * K / ms / 1e9 /
-                                                                      peaks["bf16_tflops_sustained"], 4)}
+                                                                      peaks["bf16_tflops_sustained"], 4),
+                                  "frac_of_nominal": round(2.0 * M * N * K / ms / 1e9 / NOMINAL_TENSOR_TFLOPS, 4),
+                                  "err": float(f"{err:.3e}"), "checked": err <= TOL_GEMM16}
         del a, b, c
     except Exception as e:  # noqa: BLE001
         res["gemm_bf16_deepk"] = {"error": str(e)}
@@ -438,29 +712,42 @@ def secondary(ctx, torch, stream, peaks, args):
 
 
 # ----------------------------------------------------------------------------- CPU arm
-def cpu_gemm_sample(M, N, K, rows, seed=1):
-    """fp32 BLAS product of `rows` rows of the rounded fp16 operands on all host threads."""
+def host_threads():
+    """All host cores this process may use (torchrun exports OMP_NUM_THREADS=1 to its children, which
+    would silently turn the multi-threaded CPU arm into a single-threaded one)."""
+    try:
+        return len(os.sched_getaffinity(0))
+    except Exception:
+        return os.cpu_count() or 1
+
+
+def cpu_gemm_sample(M, N, K, rows, seed=1, threads=None):
+    """fp32 BLAS product of `rows` rows of the rounded fp16 operands on `threads` host threads.
+    Returns (seconds, one value of the result, threads the BLAS pool really used)."""
     import numpy as np
+    from threadpoolctl import threadpool_info, threadpool_limits
 
     from oracle import gemm_oracle
+    threads = threads or host_threads()
     rng = np.random.default_rng(seed)
     a = (rng.standard_normal((rows, K), dtype=np.float32) / np.float32(math.sqrt(K))).astype(np.float16)
-    b = rng.standard_normal((N, K), dtype=np.float32).astype(np.float16)
-    gemm_oracle.gemm_f32_blas(a[:8], b, "fp16", False, True)  # warm the BLAS threads
-    t0 = time.perf_counter()
-    c = gemm_oracle.gemm_f32_blas(a, b, "fp16", False, True)
-    dt = time.perf_counter() - t0
-    return dt, float(c[0, 0])
+    b = (rng.standard_normal((N, K), dtype=np.float32) / np.float32(math.sqrt(K))).astype(np.float16)
+    with threadpool_limits(limits=threads):
+        used = max([p.get("num_threads", 1) for p in threadpool_info() if p.get("user_api") == "blas"] or [1])
+        gemm_oracle.gemm_f32_blas(a[:8], b, "fp16", False, True)  # warm the BLAS threads
+        t0 = time.perf_counter()
+        c = gemm_oracle.gemm_f32_blas(a, b, "fp16", False, True)
+        dt = time.perf_counter() - t0
+    return dt, float(c[0, 0]), used
 
 
 def cpu_baseline_gemm(M, N, K, budget_s=12.0):
-    cores = os.cpu_count() or 1
-    dt, _ = cpu_gemm_sample(M, N, K, 256)
+    dt, _, used = cpu_gemm_sample(M, N, K, 256)
     rate = 2.0 * 256 * N * K / dt
     rows = int(min(M, max(256, budget_s * rate / (2.0 * N * K))))
     rows = max(256, rows // 256 * 256)
-    dt, _ = cpu_gemm_sample(M, N, K, rows)
-    return {"value": round(2.0 * rows * N * K / dt / 1e12, 4), "unit": "TFLOP/s", "cores": cores, "kind": "port",
+    dt, _, used = cpu_gemm_sample(M, N, K, rows)
+    return {"value": round(2.0 * rows * N * K / dt / 1e12, 4), "unit": "TFLOP/s", "cores": used, "kind": "port",
             "sample": f"{rows} of {M} rows of the 4096^3 fp16 GEMM, numpy fp32 BLAS over the rounded inputs, "
                       f"conversion included, {dt:.2f} s"}
 
@@ -472,8 +759,7 @@ def run_reference(args):
     if rank != 0:
         return
     M = N = K = 4096
-    cores = os.cpu_count() or 1
-    dt, _ = cpu_gemm_sample(M, N, K, 256)
+    dt, _, used = cpu_gemm_sample(M, N, K, 256)
     rate = 2.0 * 256 * N * K / dt
     total_steps = args.steps + args.warmup
     rows = int(min(M, max(256, (120.0 / max(1, total_steps)) * rate / (2.0 * N * K))))
@@ -483,18 +769,74 @@ def run_reference(args):
     times = [cpu_gemm_sample(M, N, K, rows)[0] for _ in range(args.steps)]
     total = sum(times)
     value = 2.0 * rows * N * K * args.steps / total / 1e12
-    sample = f"each step = {rows} of {M} rows of the 4096^3 fp16 GEMM (numpy fp32 BLAS, all host threads)"
+    sample = f"each step = {rows} of {M} rows of the 4096^3 fp16 GEMM (numpy fp32 BLAS, {used} host threads)"
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": round(value, 4), "unit": "TFLOP/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(1e3 * total / args.steps * (M / rows), 3),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp32", "data": "synthetic",
-        "config": {"workload": "fp16 GEMM M=N=K=4096, A row-major, B column-major (NT), fp32 accumulate",
+        "config": {"workload": WORKLOAD,
                    "note": "CPU oracle port on the host cores; ms_per_step is scaled to the full 4096 rows"},
-        "cpu_baseline": {"value": round(value, 4), "unit": "TFLOP/s", "cores": cores, "kind": "port",
+        "cpu_baseline": {"value": round(value, 4), "unit": "TFLOP/s", "cores": used, "kind": "port",
                          "sample": sample},
+        "threads_used": used,
         "e2e": {"value": round(value, 4), "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }), flush=True)
+
+
+def run_case(args):
+    """`--case`: ONE kernel on a profiling-sized problem, a few launches, nothing else on the device
+    (the command the ncu summaries under profiles/ are made with).  Run plainly it prints the
+    CUDA-event time of each launch."""
+    import torch
+
+    from frisk_b200 import capi
+    torch.cuda.set_device(0)
+    ctx = capi.Context(0)
+    stream = torch.cuda.current_stream().cuda_stream
+    if args.case in ("tcgen05", "skinny", "simt"):
+        if args.case == "tcgen05":
+            M, N, K = args.m or 8192, args.n or 4096, args.k or 4096
+            a = device_normal(torch, (M, K), torch.float16, 1 / math.sqrt(K), 1)
+            b = device_normal(torch, (N, K), torch.float16, 1 / math.sqrt(K), 2)
+            c = torch.empty(M, N, device="cuda", dtype=torch.float16)
+            desc = capi.gemm_desc(M, N, K, "fp16", "fp16", False, True)
+            work, unit = 2.0 * M * N * K / 1e12, "TFLOP"
+        elif args.case == "skinny":
+            M, N, K = args.m or 16, args.n or 28672, args.k or 8192
+            a = device_normal(torch, (M, K), torch.bfloat16, 1.0, 1)
+            b = device_normal(torch, (N, K), torch.bfloat16, 0.02, 2)
+            c = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+            desc = capi.gemm_desc(M, N, K, "bf16", "bf16", False, True)
+            work, unit = (N * K + M * K + M * N) * 2 / 1e9, "GB"
+        else:
+            M, N, K = args.m or 1024, args.n or 1024, args.k or 1024
+            a = torch.rand(M, K, device="cuda") * 2 - 1
+            b = torch.rand(K, N, device="cuda") * 2 - 1
+            c = torch.empty(M, N, device="cuda")
+            desc = capi.gemm_desc(M, N, K, "fp32", "fp32")
+            work, unit = 2.0 * M * N * K / 1e12, "TFLOP"
+        fn = lambda: ctx.gemm(desc, a.data_ptr(), b.data_ptr(), c.data_ptr(), stream=stream)  # noqa: E731
+    else:
+        B, H, S, D = 1, args.heads, args.m or 4096, 128
+        q, k, v = (device_normal(torch, (B, H, S, D), torch.bfloat16, 1.0, 3 + t) for t in range(3))
+        o = torch.empty_like(q)
+        desc = capi.attn_desc(B, H, S, S, D, 1 / math.sqrt(D), True, "bf16")
+        work, unit = 4.0 * B * H * S * S * D / 2 / 1e12, "TFLOP"
+        fn = lambda: ctx.attention_fwd(desc, q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),  # noqa: E731
+                                       stream=stream)
+    times = []
+    for _ in range(args.launches):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1))
+    ctx.check(stream)
+    for t in times:
+        print(f"{args.case}: {t * 1e3:.1f} us  {work / (t * 1e-3):.1f} {unit}/s")
+    ctx.close()
 
 
 def main():
@@ -504,9 +846,22 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-secondary", action="store_true", help="skip the informational extra workloads")
+    ap.add_argument("--case", choices=["tcgen05", "skinny", "simt", "attention"],
+                    help="run ONE kernel on a profiling-sized problem instead of the benchmark")
+    ap.add_argument("--launches", type=int, default=4)
+    ap.add_argument("--m", type=int, default=0)
+    ap.add_argument("--n", type=int, default=0)
+    ap.add_argument("--k", type=int, default=0)
+    ap.add_argument("--heads", type=int, default=64)
     args = ap.parse_args()
+    if args.case:
+        return run_case(args)
     args.warmup = max(3, args.warmup) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
+        # before numpy (and its BLAS) is loaded: the CPU arm uses every core it may, whatever the launcher exported
+        n = str(host_threads())
+        for var in ("OMP_NUM_THREADS", "OPENBLAS_NUM_THREADS", "MKL_NUM_THREADS"):
+            os.environ[var] = n
         run_reference(args)
     else:
         run_ours(args)

@@ -35,33 +35,53 @@ CUtensorMapDataType tmap_dtype(int dt) {
 }
 }  // namespace
 
-int encode_tmap_2d(CUtensorMap* out, int dtype, const void* base, uint64_t inner, uint64_t outer,
-                   uint64_t outer_stride_bytes, uint32_t box_inner, uint32_t box_outer, bool swizzle128) {
+namespace {
+int encode_tiled(CUtensorMap* out, const TmapKey& k) {
   EncodeTiledFn fn = get_encode();
   if (!fn) return 999;
-  cuuint64_t dims[2] = {inner, outer};
-  cuuint64_t strides[1] = {outer_stride_bytes};
-  cuuint32_t box[2] = {box_inner, box_outer};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(out, tmap_dtype(dtype), 2, const_cast<void*>(base), dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
-                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return (int)r;
+  cuuint64_t dims[3] = {k.dims[0], k.dims[1], k.dims[2]};
+  cuuint64_t strides[2] = {k.strides[0], k.strides[1]};
+  cuuint32_t box[3] = {k.box[0], k.box[1], k.box[2]};
+  cuuint32_t estr[3] = {1, 1, 1};
+  return (int)fn(out, tmap_dtype(k.dtype), (cuuint32_t)k.rank, const_cast<void*>(k.base), dims, strides, box, estr,
+                 CU_TENSOR_MAP_INTERLEAVE_NONE, k.swizzle ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                 CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+}
+// A descriptor depends only on its key (it holds no reference to the memory besides the
+// address), so a cached one stays valid however often the buffer's contents change.
+int cached_tmap(frisk_b200_ctx* ctx, CUtensorMap* out, const TmapKey& k) {
+  if (!ctx) return encode_tiled(out, k);
+  std::lock_guard<std::mutex> lock(ctx->tmap_mu);
+  ++ctx->tmap_clock;
+  size_t oldest = 0;
+  for (size_t i = 0; i < ctx->tmaps.size(); ++i) {
+    if (ctx->tmaps[i].key == k) {
+      ctx->tmaps[i].stamp = ctx->tmap_clock;
+      *out = ctx->tmaps[i].map;
+      return 0;
+    }
+    if (ctx->tmaps[i].stamp < ctx->tmaps[oldest].stamp) oldest = i;
+  }
+  const int rc = encode_tiled(out, k);
+  if (rc) return rc;
+  TmapEntry e{k, *out, ctx->tmap_clock};
+  if (ctx->tmaps.size() < kTmapCacheEntries) ctx->tmaps.push_back(e); else ctx->tmaps[oldest] = e;
+  return 0;
+}
+}  // namespace
+
+int encode_tmap_2d(frisk_b200_ctx* ctx, CUtensorMap* out, int dtype, const void* base, uint64_t inner,
+                   uint64_t outer, uint64_t outer_stride_bytes, uint32_t box_inner, uint32_t box_outer,
+                   bool swizzle128) {
+  TmapKey k{base, {inner, outer, 1}, {outer_stride_bytes, 0}, {box_inner, box_outer, 1}, dtype, 2, swizzle128 ? 1 : 0};
+  return cached_tmap(ctx, out, k);
 }
 
-int encode_tmap_3d(CUtensorMap* out, int dtype, const void* base, uint64_t d0, uint64_t d1, uint64_t d2,
-                   uint64_t stride1_bytes, uint64_t stride2_bytes, uint32_t b0, uint32_t b1, uint32_t b2,
-                   bool swizzle128) {
-  EncodeTiledFn fn = get_encode();
-  if (!fn) return 999;
-  cuuint64_t dims[3] = {d0, d1, d2};
-  cuuint64_t strides[2] = {stride1_bytes, stride2_bytes};
-  cuuint32_t box[3] = {b0, b1, b2};
-  cuuint32_t estr[3] = {1, 1, 1};
-  CUresult r = fn(out, tmap_dtype(dtype), 3, const_cast<void*>(base), dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
-                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return (int)r;
+int encode_tmap_3d(frisk_b200_ctx* ctx, CUtensorMap* out, int dtype, const void* base, uint64_t d0, uint64_t d1,
+                   uint64_t d2, uint64_t stride1_bytes, uint64_t stride2_bytes, uint32_t b0, uint32_t b1,
+                   uint32_t b2, bool swizzle128) {
+  TmapKey k{base, {d0, d1, d2}, {stride1_bytes, stride2_bytes}, {b0, b1, b2}, dtype, 3, swizzle128 ? 1 : 0};
+  return cached_tmap(ctx, out, k);
 }
 
 // ---------------------------------------------------------------- small kernels

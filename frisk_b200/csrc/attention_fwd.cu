@@ -483,9 +483,9 @@ int launch_cfg(frisk_b200_ctx* ctx, const frisk_b200_attn_desc& d, const void* Q
   CUtensorMap tq, tk, tv;
   const int bh = d.B * d.H;
   const uint64_t row_bytes = (uint64_t)D * 2;
-  int rc = encode_tmap_3d(&tq, d.dtype_in, Q, D, d.S_q, bh, row_bytes, row_bytes * d.S_q, 64, BM, 1, true);
-  if (!rc) rc = encode_tmap_3d(&tk, d.dtype_in, K, D, d.S_kv, bh, row_bytes, row_bytes * d.S_kv, 64, BN, 1, true);
-  if (!rc) rc = encode_tmap_3d(&tv, d.dtype_in, V, D, d.S_kv, bh, row_bytes, row_bytes * d.S_kv, 64, BN, 1, true);
+  int rc = encode_tmap_3d(ctx, &tq, d.dtype_in, Q, D, d.S_q, bh, row_bytes, row_bytes * d.S_q, 64, BM, 1, true);
+  if (!rc) rc = encode_tmap_3d(ctx, &tk, d.dtype_in, K, D, d.S_kv, bh, row_bytes, row_bytes * d.S_kv, 64, BN, 1, true);
+  if (!rc) rc = encode_tmap_3d(ctx, &tv, d.dtype_in, V, D, d.S_kv, bh, row_bytes, row_bytes * d.S_kv, 64, BN, 1, true);
   if (rc) {
     ctx->last_cuda = rc;
     return FRISK_B200_E_CUDA;
@@ -508,12 +508,18 @@ int launch_cfg(frisk_b200_ctx* ctx, const frisk_b200_attn_desc& d, const void* Q
   // asks for: the registers the TMA/MMA warpgroup (128 threads) gives up must cover what the
   // two softmax warpgroups (256 threads) take, or the kernel would never start.  Checked
   // against the compiled register count before every launch.
-  cudaFuncAttributes fa;
-  FB_CUDA(ctx, cudaFuncGetAttributes(&fa, kern));
-  if (fa.numRegs < kRegsOther || fa.numRegs > kRegsSoftmax ||
-      (fa.numRegs - kRegsOther) * 128 < (kRegsSoftmax - fa.numRegs) * 256)
-    return FRISK_B200_E_UNSUPPORTED;
-  FB_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
+  static PerDeviceOnce set_up;  // one per instantiation; a failed check is repeated (and fails) every call
+  const int bad = set_up(ctx->device, [&] {
+    cudaFuncAttributes fa;
+    if (cudaFuncGetAttributes(&fa, kern) != cudaSuccess) return (int)FRISK_B200_E_CUDA;
+    if (fa.numRegs < kRegsOther || fa.numRegs > kRegsSoftmax ||
+        (fa.numRegs - kRegsOther) * 128 < (kRegsSoftmax - fa.numRegs) * 256)
+      return (int)FRISK_B200_E_UNSUPPORTED;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal) != cudaSuccess)
+      return (int)FRISK_B200_E_CUDA;
+    return 0;
+  });
+  if (bad) return bad;
   kern<<<(unsigned)p.total_ctas, kThreads, L::kTotal, s>>>(tq, tk, tv, p);
   FB_CUDA(ctx, cudaGetLastError());
   return 0;

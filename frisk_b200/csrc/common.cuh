@@ -8,6 +8,7 @@
 #include <stddef.h>
 #include <stdint.h>
 
+#include <atomic>
 #include <map>
 #include <mutex>
 #include <string>
@@ -22,6 +23,43 @@ constexpr int kNumSMsDefault = 148;
 struct StagingBuffer {
   void* ptr = nullptr;
   size_t bytes = 0;
+};
+
+// One encoded TMA descriptor and everything that determined it.  The context keeps the most
+// recently used ones, so a caller that launches the same operands again (the normal case: a
+// weight matrix, a preallocated activation buffer) pays the driver's encode call once.
+struct TmapKey {
+  const void* base;
+  uint64_t dims[3], strides[2];
+  uint32_t box[3];
+  int dtype, rank, swizzle;
+  bool operator==(const TmapKey& o) const {
+    return base == o.base && dtype == o.dtype && rank == o.rank && swizzle == o.swizzle && dims[0] == o.dims[0] &&
+           dims[1] == o.dims[1] && dims[2] == o.dims[2] && strides[0] == o.strides[0] && strides[1] == o.strides[1] &&
+           box[0] == o.box[0] && box[1] == o.box[1] && box[2] == o.box[2];
+  }
+};
+struct TmapEntry {
+  TmapKey key;
+  CUtensorMap map;
+  uint64_t stamp;
+};
+constexpr size_t kTmapCacheEntries = 64;
+constexpr int kMaxDevices = 64;
+
+// Per-kernel set-up that has to happen once per device (opting in to large dynamic shared
+// memory, an occupancy query): `run` returns 0 on success, and then never runs again for
+// that device.  Two threads may both run it the first time; the calls are idempotent.
+struct PerDeviceOnce {
+  std::atomic<int> done[kMaxDevices] = {};
+  template <typename F>
+  int operator()(int device, F&& run) {
+    if (device < 0 || device >= kMaxDevices) return run();
+    if (done[device].load(std::memory_order_acquire)) return 0;
+    const int rc = run();
+    if (rc == 0) done[device].store(1, std::memory_order_release);
+    return rc;
+  }
 };
 
 }  // namespace fb
@@ -41,6 +79,9 @@ struct frisk_b200_ctx {
   cudaStream_t out_stream = nullptr;
   cudaEvent_t ev[24] = {};
   std::mutex mu;
+  std::mutex tmap_mu;
+  std::vector<fb::TmapEntry> tmaps;  // encoded TMA descriptors, most recently used (see TmapKey)
+  uint64_t tmap_clock = 0;
 };
 
 namespace fb {
@@ -179,11 +220,13 @@ int launch_attention_fwd(frisk_b200_ctx* ctx, const frisk_b200_attn_desc& d, con
 
 int launch_convert_f32(const float* src, void* dst, int64_t n, int dtype, cudaStream_t s);
 
-// TMA descriptor encode through the driver entry point (no link-time libcuda dependency)
-int encode_tmap_2d(CUtensorMap* out, int dtype, const void* base, uint64_t inner, uint64_t outer,
-                   uint64_t outer_stride_bytes, uint32_t box_inner, uint32_t box_outer, bool swizzle128);
-int encode_tmap_3d(CUtensorMap* out, int dtype, const void* base, uint64_t d0, uint64_t d1, uint64_t d2,
-                   uint64_t stride1_bytes, uint64_t stride2_bytes, uint32_t b0, uint32_t b1, uint32_t b2,
+// TMA descriptors, encoded through the driver entry point (no link-time libcuda dependency) and
+// kept in the context's cache (ctx may be NULL: encode without caching)
+int encode_tmap_2d(frisk_b200_ctx* ctx, CUtensorMap* out, int dtype, const void* base, uint64_t inner,
+                   uint64_t outer, uint64_t outer_stride_bytes, uint32_t box_inner, uint32_t box_outer,
                    bool swizzle128);
+int encode_tmap_3d(frisk_b200_ctx* ctx, CUtensorMap* out, int dtype, const void* base, uint64_t d0, uint64_t d1,
+                   uint64_t d2, uint64_t stride1_bytes, uint64_t stride2_bytes, uint32_t b0, uint32_t b1,
+                   uint32_t b2, bool swizzle128);
 
 }  // namespace fb

@@ -324,7 +324,14 @@ int launch_typed(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc& d, const Skinn
                  const void* B, void* C, void* ws, cudaStream_t s) {
   GemmDims g = resolve_dims(d);
   auto kern = gemm_skinny_kernel<T, TO>;
-  FB_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p.smem));
+  // the opt-in is made once per device for the largest size any plan uses
+  static PerDeviceOnce opt_in;
+  int device = 0;
+  FB_CUDA(ctx, cudaGetDevice(&device));
+  if (opt_in(device, [&] {
+        return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxSmem) == cudaSuccess ? 0 : 1;
+      }))
+    return FRISK_B200_E_CUDA;
   unsigned char* w = static_cast<unsigned char*>(ws);
   kern<<<p.grid, kThreads, p.smem, s>>>(static_cast<const T*>(A), static_cast<const T*>(B), static_cast<TO*>(C),
                                         (int)g.M, (int)g.N, (int)g.K, g.lda, g.ldb, g.ldc, p.S, p.kslice,

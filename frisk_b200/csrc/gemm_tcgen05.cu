@@ -18,7 +18,6 @@
 // (lib/Dialect/Frisk/Target/SM90/SM90GemmConstraints.cpp:121-138); TMA writes them directly.
 // No TMA load uses cluster multicast.
 #include "common.cuh"
-#include <cstdlib>
 
 #include "gemm_common.cuh"
 #include "ptx.cuh"
@@ -268,19 +267,23 @@ int launch_cfg(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc& d, const void* A
   int rc;
   // A: K-major -> dims {K, M}, box {64, 128};  MN-major (stored [K,M]) -> dims {M, K}, box {64, 64}
   if (A_MN)
-    rc = encode_tmap_2d(&ta, d.dtype_ab, A, (uint64_t)g.M, (uint64_t)g.K, (uint64_t)g.lda * 2, 64, BK, true);
+    rc = encode_tmap_2d(ctx, &ta, d.dtype_ab, A, (uint64_t)g.M, (uint64_t)g.K, (uint64_t)g.lda * 2, 64, BK, true);
   else
-    rc = encode_tmap_2d(&ta, d.dtype_ab, A, (uint64_t)g.K, (uint64_t)g.M, (uint64_t)g.lda * 2, BK, BM, true);
+    rc = encode_tmap_2d(ctx, &ta, d.dtype_ab, A, (uint64_t)g.K, (uint64_t)g.M, (uint64_t)g.lda * 2, BK, BM, true);
   if (rc) { if (ctx) ctx->last_cuda = rc; return FRISK_B200_E_CUDA; }
   if (B_MN)
-    rc = encode_tmap_2d(&tb, d.dtype_ab, B, (uint64_t)g.N, (uint64_t)g.K, (uint64_t)g.ldb * 2, 64, BK, true);
+    rc = encode_tmap_2d(ctx, &tb, d.dtype_ab, B, (uint64_t)g.N, (uint64_t)g.K, (uint64_t)g.ldb * 2, 64, BK, true);
   else
-    rc = encode_tmap_2d(&tb, d.dtype_ab, B, (uint64_t)g.K, (uint64_t)g.N, (uint64_t)g.ldb * 2, BK, 128, true);
+    rc = encode_tmap_2d(ctx, &tb, d.dtype_ab, B, (uint64_t)g.K, (uint64_t)g.N, (uint64_t)g.ldb * 2, BK, 128, true);
   if (rc) { if (ctx) ctx->last_cuda = rc; return FRISK_B200_E_CUDA; }
 
   auto kern = gemm_tcgen05_kernel<TO, BN, BF16, A_MN, B_MN>;
   using L = SmemLayout<BN>;
-  FB_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
+  static PerDeviceOnce opt_in;  // one per instantiation
+  if (opt_in(ctx->device, [&] {
+        return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal) == cudaSuccess ? 0 : 1;
+      }))
+    return FRISK_B200_E_CUDA;
   int tiles = (int)(((g.M + BM - 1) / BM) * ((g.N + BN - 1) / BN));
   int grid = tiles < ctx->num_sms ? tiles : ctx->num_sms;
   // A partial last wave of at most grid/2 tiles runs as twice as many half-width items: the
@@ -292,9 +295,6 @@ int launch_cfg(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc& d, const void* A
     n_items = n_full + 2 * rem;
   }
   int prefetch = kPrefetchAhead;
-  if (const char* e = getenv("FRISK_B200_GEMM_PREFETCH")) prefetch = atoi(e);
-  if (const char* e = getenv("FRISK_B200_GEMM_NO_TAIL_SPLIT"))
-    if (e[0] == '1') n_full = n_items = tiles;
   int vec_c = aligned16(C) && (g.ldc * sizeof(TO)) % 16 == 0;
   kern<<<grid, kThreads, L::kTotal, s>>>(ta, tb, static_cast<TO*>(C), (int)g.M, (int)g.N, (int)g.K, g.ldc,
                                          d.clear_accum ? 0 : 1, vec_c, n_full, n_items, prefetch, ctx->d_status);

@@ -17,7 +17,6 @@
 //
 //   warp 0    TMA producer (both CTAs)         warp 1   MMA issuer (leader CTA only)
 //   warps 2-5 epilogue (both CTAs, own rows)
-#include <cstdlib>
 
 #include "common.cuh"
 #include "gemm_common.cuh"
@@ -435,8 +434,7 @@ TailPlan make_tail_plan(const frisk_b200_gemm_desc& d, int pairs_available) {
   t.n_full = t.n_items = tiles;
   int rem = tiles % t.pairs;
   int num_kb = (int)((g.K + BK - 1) / BK);
-  const char* e = getenv("FRISK_B200_GEMM_NO_TAIL_SPLIT");
-  if (tiles > t.pairs && rem > 0 && 2 * rem <= t.pairs && num_kb >= 8 && !(e && e[0] == '1')) {
+  if (tiles > t.pairs && rem > 0 && 2 * rem <= t.pairs && num_kb >= 8) {
     t.tail_tiles = rem;
     t.n_full = tiles - rem;
     t.n_items = t.n_full + 2 * rem;
@@ -456,19 +454,18 @@ int launch_cfg2(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc& d, const void* 
   CUtensorMap ta, tb;
   int rc;
   if (A_MN)
-    rc = encode_tmap_2d(&ta, d.dtype_ab, A, (uint64_t)g.M, (uint64_t)g.K, (uint64_t)g.lda * 2, 64, BK, true);
+    rc = encode_tmap_2d(ctx, &ta, d.dtype_ab, A, (uint64_t)g.M, (uint64_t)g.K, (uint64_t)g.lda * 2, 64, BK, true);
   else
-    rc = encode_tmap_2d(&ta, d.dtype_ab, A, (uint64_t)g.K, (uint64_t)g.M, (uint64_t)g.lda * 2, BK, BMC, true);
+    rc = encode_tmap_2d(ctx, &ta, d.dtype_ab, A, (uint64_t)g.K, (uint64_t)g.M, (uint64_t)g.lda * 2, BK, BMC, true);
   if (rc) { ctx->last_cuda = rc; return FRISK_B200_E_CUDA; }
   if (B_MN)
-    rc = encode_tmap_2d(&tb, d.dtype_ab, B, (uint64_t)g.N, (uint64_t)g.K, (uint64_t)g.ldb * 2, 64, BK, true);
+    rc = encode_tmap_2d(ctx, &tb, d.dtype_ab, B, (uint64_t)g.N, (uint64_t)g.K, (uint64_t)g.ldb * 2, 64, BK, true);
   else
-    rc = encode_tmap_2d(&tb, d.dtype_ab, B, (uint64_t)g.K, (uint64_t)g.N, (uint64_t)g.ldb * 2, BK, BNC, true);
+    rc = encode_tmap_2d(ctx, &tb, d.dtype_ab, B, (uint64_t)g.K, (uint64_t)g.N, (uint64_t)g.ldb * 2, BK, BNC, true);
   if (rc) { ctx->last_cuda = rc; return FRISK_B200_E_CUDA; }
 
   auto kern = gemm_tcgen05_2cta_kernel<TO, BF16, A_MN, B_MN, MODE>;
   constexpr int kSmemBytes = MODE == kPush ? Smem2::kTotalPush : Smem2::kTotal;
-  FB_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
   cudaLaunchConfig_t cfg = {};
   cudaLaunchAttribute attr[2];
   attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -483,8 +480,19 @@ int launch_cfg2(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc& d, const void* 
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   cfg.gridDim = dim3(2 * (ctx->num_sms / 2));
-  int max_clusters = 0;
-  FB_CUDA(ctx, cudaOccupancyMaxActiveClusters(&max_clusters, kern, &cfg));
+  // once per device and instantiation: the shared-memory opt-in and how many CTA pairs fit the device
+  static PerDeviceOnce set_up;
+  static std::atomic<int> pairs_on_device[kMaxDevices];
+  if (ctx->device < 0 || ctx->device >= kMaxDevices) return FRISK_B200_E_ARG;
+  if (set_up(ctx->device, [&] {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess) return 1;
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) return 1;
+        pairs_on_device[ctx->device].store(n);
+        return 0;
+      }))
+    return FRISK_B200_E_CUDA;
+  int max_clusters = pairs_on_device[ctx->device].load();
   if (max_clusters < 1) return FRISK_B200_E_UNSUPPORTED;
   if (max_clusters > kPairsAssumed) max_clusters = kPairsAssumed;
   TailPlan tp = make_tail_plan(d, max_clusters);
@@ -528,7 +536,6 @@ int launch_major2(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc& d, const void
 
 // The pair kernel pays when there are enough 256 x 256 tiles to fill the machine's CTA pairs.
 bool tcgen05_2cta_preferred(const frisk_b200_gemm_desc& d) {
-  if (const char* e = getenv("FRISK_B200_GEMM_PAIR")) return e[0] == '1';
   const int64_t tiles = ((d.M + BM2 - 1) / BM2) * ((d.N + BN2 - 1) / BN2);
   return tiles >= kNumSMsDefault / 2;
 }
