@@ -312,7 +312,10 @@ def run_ours(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_s = float(t.item())
     e2e_value = world * flop * e2e_steps / e2e_s / 1e12
-    e2e_same_bits = bool(torch.equal(hc.view(torch.int16), c_seeded.cpu().view(torch.int16)))
+    # (not bit-identical to the device-resident path: the host entry multiplies four row panels, whose
+    # tiles meet the K-split tail wave differently; both are checked against the oracle)
+    e2e_err = rel_err_gemm_sample(torch, sets[0][0], sets[0][1], hc.cuda(), sample_indices(M, 64, 15),
+                                  sample_indices(N, 256, 16))
     link = host_link_rates(torch, dist, world, ha, hc)
 
     splitk_res = sharded_res = None
@@ -338,7 +341,7 @@ def run_ours(args):
                        "pct_of_nominal_dense_peak": round(100 * value / world / NOMINAL_TENSOR_TFLOPS, 2)},
             "e2e": {"value": round(e2e_value, 3), "unit": "TFLOP/s", "h2d_bytes_per_step": 2 * M * K * 2,
                     "d2h_bytes_per_step": M * N * 2, "steps": e2e_steps,
-                    "same_bits_as_device_path": e2e_same_bits, "host_link": link},
+                    "err": float(f"{e2e_err:.3e}"), "checked": e2e_err <= TOL_GEMM16, "host_link": link},
             "gpu_launches": args.steps,
             "clocks": clocks,
             "checked": {"err": float(f"{headline_err:.3e}"), "tolerance": TOL_GEMM16, "ok": headline_err <= TOL_GEMM16,

@@ -229,9 +229,9 @@ def test_launch_contract_refusals(ctx):
     import torch
     B, H, S, D = 1, 2, 256, 128
     n = B * H * S * D
-    buf = torch.zeros(3 * n, dtype=torch.bfloat16, device="cuda")
-    q, k, v = (buf[i * n:(i + 1) * n] for i in range(3))
-    o = torch.zeros(n + 64, dtype=torch.bfloat16, device="cuda")
+    gap = 128  # elements between the tensors, so that a shifted input still ends before the next buffer
+    buf = torch.zeros(4 * (n + gap), dtype=torch.bfloat16, device="cuda")
+    q, k, v, o = (buf[i * (n + gap):i * (n + gap) + n] for i in range(4))
     desc = capi.attn_desc(B, H, S, S, D, D ** -0.5, True, "bf16")
     s = torch.cuda.current_stream().cuda_stream
     ctx.attention_fwd(desc, q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), stream=s)  # disjoint: accepted
