@@ -12,9 +12,9 @@ The strong-scaled forms of every workload that shards (one 4096^3 product cut in
 blocks, the skinny GEMM cut along N, the attention cut along batch x head, the deep-K GEMM
 cut along K with its one exchange step) are timed AND checked in `secondary`.
 
-Timing: CUDA events on the launching stream around every step, W >= 3 warm-up steps,
-inputs rotate through buffer sets larger than L2 so no step finds its operands cached,
-barrier + synchronize on both sides of the timed region, max over ranks.
+Timing: one pair of CUDA events on the launching stream around the K timed steps, W >= 3
+warm-up steps, inputs rotate through buffer sets larger than L2 so no step finds its operands
+cached, barrier + synchronize on both sides of the timed region, max over ranks.
 
 Keys beyond the basic contract: `e2e` (same GEMM through the host-buffer C-ABI entry
 point, pinned host memory, copies inside the timed region), `roofline`, `cpu_baseline`
@@ -161,7 +161,11 @@ def dist_env():
 
 
 def time_steps(fn, steps, warmup, torch, dist, world):
-    """fn(i) launches step i on the current stream.  Returns (total ms max over ranks, per-step ms list)."""
+    """fn(i) launches step i on the current stream.  The K timed steps are enqueued back to back and
+    bracketed by ONE pair of CUDA events on that stream (a kernel launched with programmatic stream
+    serialization may then overlap its set-up with the tail of the step before it, as it does in a real
+    stream of GEMMs; an event between every two steps would forbid that).  Returns (total ms, max over
+    ranks; per-step ms list; wall-clock window)."""
     for i in range(warmup):
         fn(i)
     torch.cuda.synchronize()
@@ -169,18 +173,18 @@ def time_steps(fn, steps, warmup, torch, dist, world):
         dist.barrier()
     torch.cuda.synchronize()
     t_wall0 = time.time()
-    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
     for i in range(steps):
-        evs[i][0].record()
         fn(warmup + i)
-        evs[i][1].record()
+    e1.record()
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize()
     t_wall1 = time.time()
-    per = [a.elapsed_time(b) for a, b in evs]
-    total = float(sum(per))
+    total = float(e0.elapsed_time(e1))
+    per = [total / steps] * steps
     if world > 1:
         t = torch.tensor([total], dtype=torch.float64, device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)

@@ -195,7 +195,7 @@ int prepare_owned_skinny_ws(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc& d, 
   void* before = ctx->stage[3].ptr;
   int rc = ensure_stage(ctx, 3, need, true, s);
   if (rc) return rc;
-  uint64_t sig = skinny_layout_signature(d);
+  uint64_t sig = (uint64_t)skinny_control_bytes(d) | (1ull << 63);
   if (ctx->stage[3].ptr != before) {
     ctx->ws_signature = sig;  // fresh and fully zeroed
   } else if (ctx->ws_signature != sig) {

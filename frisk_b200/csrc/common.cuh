@@ -166,16 +166,17 @@ inline GemmExtents gemm_extents(const frisk_b200_gemm_desc& d) {
 int launch_gemm_simt_f32(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc& d, const float* A, const float* B,
                          float* C, cudaStream_t s);
 
+// Decode-shape GEMM (gemm_skinny.cu).  Its scratch begins with one ticket per 128-column tile; the
+// kernel leaves them at zero, so they need clearing only when the scratch was last used with
+// another layout (another kernel's partial sums may lie where this one keeps tickets):
+// skinny_control_bytes is the size of that prefix and also identifies the layout.
 size_t skinny_workspace_bytes(const frisk_b200_gemm_desc& d);
-// bytes at the start of the workspace that hold control words (must be zero before a launch)
-// and a value that identifies their layout: a workspace last used with another layout must
-// have that prefix cleared again, because another kernel's partial sums may lie where this one keeps its
-// queue counters.
 size_t skinny_control_bytes(const frisk_b200_gemm_desc& d);
-uint64_t skinny_layout_signature(const frisk_b200_gemm_desc& d);
 bool skinny_supported(const frisk_b200_gemm_desc& d);
+// `ctx` may be NULL (the entry that allocates nothing has no context): `status` then names the
+// device word in which a wait that ran out is recorded.
 int launch_gemm_skinny(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc& d, const void* A, const void* B, void* C,
-                       void* ws, size_t ws_bytes, cudaStream_t s);
+                       void* ws, size_t ws_bytes, cudaStream_t s, unsigned* status = nullptr);
 
 bool tcgen05_supported(const frisk_b200_gemm_desc& d);
 int launch_gemm_tcgen05(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc& d, const void* A, const void* B,

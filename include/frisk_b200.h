@@ -38,7 +38,7 @@ enum {
   FRISK_B200_ALGO_AUTO = 0,
   FRISK_B200_ALGO_SIMT_F32 = 1, /* fp32 CUDA-core GEMM                                   */
   FRISK_B200_ALGO_TCGEN05 = 2,  /* fp16/bf16 tcgen05 + TMEM + TMA ring, one CTA per tile */
-  FRISK_B200_ALGO_SKINNY = 3,   /* M<=16 weight-streaming GEMM, split-K across CTAs      */
+  FRISK_B200_ALGO_SKINNY = 3,   /* M<=16: weights streamed by TMA into tcgen05, stream-K  */
   FRISK_B200_ALGO_TCGEN05_PAIR = 4 /* tcgen05 with CTA pairs (cta_group::2), 256x256 tiles */
 };
 
@@ -154,8 +154,9 @@ int frisk_b200_gemm_host(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc* desc, 
  * HBM at start-up, so a cudaMalloc made now would fail, and latency-critical loops that cannot
  * take the device-wide synchronisation of cudaMalloc / cudaFree.  It has no counterpart in the
  * reference (whose kernels need no scratch); it needs no context either, because creating one
- * allocates.  The kernel's split-K scratch is a fixed 8 MiB array inside the library's device
- * image (every GPU that loads the library holds those 8 MiB until the process exits).
+ * allocates.  The kernel's stream-K scratch (tickets and fp32 partial sums) is a fixed 8 MiB array
+ * inside the library's device image (every GPU that loads the library holds those 8 MiB until the
+ * process exits).
  *  - Problems whose scratch (frisk_b200_gemm_workspace_bytes) exceeds 8 MiB are refused with
  *    FRISK_B200_E_TOO_LARGE; nothing is launched.
  *  - The first call on a device looks up that device's address of the array; make that first

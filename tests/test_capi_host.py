@@ -79,10 +79,9 @@ def test_kernel_selection_and_workspace():
     assert sel(capi.gemm_desc(64, 64, 64, "fp32", "fp16")) == -2
     assert sel(capi.gemm_desc(0, 64, 64, "fp32")) == -1
     assert sel(capi.gemm_desc(64, 64, 64, "fp16", algo=capi.ALGO_SIMT_F32)) == -6
-    # decode shapes whose K slice of X cannot fit shared memory even with the deepest split go to tcgen05
-    assert sel(capi.gemm_desc(16, 4096, 65536, "bf16", trans_b=True)) == capi.ALGO_SKINNY
-    assert sel(capi.gemm_desc(16, 4096, 131072, "bf16", trans_b=True)) == capi.ALGO_TCGEN05
-    assert sel(capi.gemm_desc(16, 4096, 131072, "bf16", trans_b=True, algo=capi.ALGO_SKINNY)) == -6
+    # the decode kernel streams K through a ring, so no K is too deep for it; M > 16 is
+    assert sel(capi.gemm_desc(16, 4096, 131072, "bf16", trans_b=True)) == capi.ALGO_SKINNY
+    assert sel(capi.gemm_desc(17, 4096, 8192, "bf16", trans_b=True, algo=capi.ALGO_SKINNY)) == -6
 
 
 def test_static_scratch_entry_host_side_refusals():
@@ -90,8 +89,10 @@ def test_static_scratch_entry_host_side_refusals():
     for, one beyond its fixed scratch, and an output that overlaps an input."""
     lib = capi.load()
     call = lambda d, a, b, c: lib.frisk_b200_gemm_skinny_static(0, ctypes.byref(d), a, b, c, None)  # noqa: E731
-    assert call(capi.gemm_desc(16, 4096, 131072, "bf16", trans_b=True), 0x1000, 0x2000, 0x3000) == -6
-    assert call(capi.gemm_desc(16, 200000, 8192, "bf16", trans_b=True), 0x1000, 0x2000, 0x3000) == -9
+    assert call(capi.gemm_desc(64, 4096, 8192, "bf16", trans_b=True), 0x1000, 0x2000, 0x3000) == -6
+    huge = capi.gemm_desc(16, 200_000_000, 64, "bf16", trans_b=True)   # one ticket per 128 columns: > 8 MiB
+    assert lib.frisk_b200_gemm_workspace_bytes(ctypes.byref(huge)) > 8 << 20
+    assert call(huge, 0x1000, 0x2000, 0x3000) == -9
     d = capi.gemm_desc(16, 1024, 1024, "bf16", trans_b=True)
     a_bytes, b_bytes = 16 * 1024 * 2, 1024 * 1024 * 2
     base = 0x10000000

@@ -13,6 +13,7 @@ from tests.util import Guarded, to_device, to_host
 pytestmark = pytest.mark.gpu
 TOL = {"fp32": 1e-3, "fp16": 5e-3, "bf16": 5e-3}
 TC_ALGOS = [capi.ALGO_TCGEN05, capi.ALGO_TCGEN05_PAIR]
+SKINNY_ALGOS = [capi.ALGO_SKINNY]
 
 
 @pytest.fixture(scope="module")
@@ -240,26 +241,32 @@ def test_deepk_config(ctx):
 
 
 # ------------------------------------------------------------------ skinny
-def test_skinny_config(ctx):
+@pytest.mark.parametrize("algo", SKINNY_ALGOS)
+def test_skinny_config(ctx, algo):
     spec = inputs.WORKLOADS["gemm_bf16_skinny"]
-    err = check(ctx, spec["M"], spec["N"], spec["K"], "bf16", "bf16", False, True, spec["seed"], dist="act_weight")
+    err = check(ctx, spec["M"], spec["N"], spec["K"], "bf16", "bf16", False, True, spec["seed"], dist="act_weight",
+                algo=algo)
     assert err < 4e-3
 
 
+@pytest.mark.parametrize("algo", SKINNY_ALGOS)
 @pytest.mark.parametrize("dtype", ["fp16", "bf16"])
-def test_skinny_shapes(ctx, dtype):
-    for (M, N, K) in ((16, 64, 256), (1, 8, 8), (7, 100, 264), (16, 1000, 4096), (13, 2056, 9000 // 8 * 8)):
-        check(ctx, M, N, K, dtype, dtype, False, True, 31, algo=capi.ALGO_SKINNY, dist="act_weight")
+def test_skinny_shapes(ctx, dtype, algo):
+    # tiny, ragged in every extent, fewer tiles than SMs (a tile's K shared by many CTAs), one output shard of 8 GPUs
+    for (M, N, K) in ((16, 64, 256), (1, 8, 8), (7, 100, 264), (16, 1000, 4096), (13, 2056, 9000 // 8 * 8),
+                      (16, 3584, 8192), (3, 130, 72)):
+        check(ctx, M, N, K, dtype, dtype, False, True, 31, algo=algo, dist="act_weight")
 
 
-def test_skinny_f32_out_accumulate_and_repeat(ctx):
-    check(ctx, 16, 512, 16384, "bf16", "fp32", False, True, 32, algo=capi.ALGO_SKINNY, dist="act_weight")
-    check(ctx, 5, 264, 2048, "fp16", "fp16", False, True, 33, accumulate=True, algo=capi.ALGO_SKINNY)
-    # the queue counters must be clean after every launch: identical bits on repeats
+@pytest.mark.parametrize("algo", SKINNY_ALGOS)
+def test_skinny_f32_out_accumulate_and_repeat(ctx, algo):
+    check(ctx, 16, 512, 16384, "bf16", "fp32", False, True, 32, algo=algo, dist="act_weight")
+    check(ctx, 5, 264, 2048, "fp16", "fp16", False, True, 33, accumulate=True, algo=algo)
+    # the control words must be clean after every launch: identical bits on repeats
     a, b = inputs.gemm_inputs(16, 4096, 8192, "bf16", False, True, 34, "act_weight")
-    first, _ = run_gemm(ctx, a, b, "bf16", "bf16", 16, 4096, 8192, False, True, algo=capi.ALGO_SKINNY)
+    first, _ = run_gemm(ctx, a, b, "bf16", "bf16", 16, 4096, 8192, False, True, algo=algo)
     for _ in range(3):
-        again, ok = run_gemm(ctx, a, b, "bf16", "bf16", 16, 4096, 8192, False, True, algo=capi.ALGO_SKINNY)
+        again, ok = run_gemm(ctx, a, b, "bf16", "bf16", 16, 4096, 8192, False, True, algo=algo)
         assert ok and np.array_equal(first, again)
 
 

@@ -43,8 +43,8 @@ def _both(ctx, M, N, K, dtype, seed):
 def test_static_scratch_entry_matches_ordinary_entry_twice():
     ctx = capi.Context(0)
     try:
-        _both(ctx, 16, 1024, 8192, "bf16", 51)   # split-K, small partial-sum area
-        _both(ctx, 13, 6152, 8192, "bf16", 52)   # larger layout over the first call's partial sums
+        _both(ctx, 16, 1024, 8192, "bf16", 51)   # 8 tiles: every tile's K is shared by many CTAs
+        _both(ctx, 13, 28672, 1024, "bf16", 52)  # 224 tiles: more tickets, lying over the first call's partial sums
         _both(ctx, 16, 1024, 8192, "bf16", 51)   # and back
     finally:
         ctx.close()
@@ -52,7 +52,7 @@ def test_static_scratch_entry_matches_ordinary_entry_twice():
 
 def test_static_scratch_entry_refuses_oversize_and_bad_layout():
     lib = capi.load()
-    big = capi.gemm_desc(16, 200000, 8192, "bf16", "bf16", False, True)
+    big = capi.gemm_desc(16, 200_000_000, 64, "bf16", "bf16", False, True)  # one ticket per 128 columns
     assert lib.frisk_b200_gemm_workspace_bytes(big) > 8 << 20
     assert lib.frisk_b200_gemm_skinny_static(0, ctypes.byref(big), 16, 16, 16, None) == -9
     assert "capacity" in capi.strerror(-9)
