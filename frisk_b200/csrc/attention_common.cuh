@@ -9,7 +9,7 @@ namespace attn {
 
 constexpr int BM = 128;        // query rows per tile (two tiles per CTA)
 constexpr int BN = 128;        // keys per K/V tile
-constexpr int kThreads = 384;  // warps 0-3, 4-7: softmax groups; warp 8: TMA; warp 9: MMA; 10-11 idle
+constexpr int kThreads = 384;  // warps 0-3, 4-7: softmax groups; warp 8: TMA; warps 9, 10: MMA of query tile 0, 1; 11 idle
 constexpr int kRegsSoftmax = 208, kRegsOther = 72;  // per-thread register budgets after setmaxnreg
 constexpr int kWarpTma = 8, kWarpMma = 9;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units

@@ -10,9 +10,9 @@
 //
 //   * one CTA owns TWO 128-row query tiles of one (batch, head) and streams 128-key K/V tiles
 //     through a 2-stage TMA ring (K and V have separate full/empty mbarriers);
-//   * warp 8 is the TMA producer, warp 9 issues every tcgen05.mma: S_q = Q_q.K^T (SS form,
-//     both operands K-major, 128-byte swizzle) into tensor memory and O_q += P_q.V (P read
-//     from tensor memory, V as an MN-major shared-memory operand);
+//   * warp 8 is the TMA producer; warps 9 and 10 issue the tcgen05.mma of query tile 0 and 1: S_q =
+//     Q_q.K^T (SS form, both operands K-major, 128-byte swizzle) into tensor memory and O_q += P_q.V
+//     (P read from tensor memory, V as an MN-major shared-memory operand);
 //   * warps 0-3 and 4-7 are the two softmax groups: thread r owns row r of its query tile
 //     (TMEM lane r), so row max / row sum need no shuffles.  The two groups alternate, so
 //     the tensor core works on one tile's MMAs while the other group exponentiates;
@@ -24,6 +24,8 @@
 // TMEM columns: S0 [0,128) S1 [128,256) O0 [256,256+D) O1 [384,384+D); P_q aliases the first
 // 64 columns of S_q (two 16-bit values per column).
 // Every mbarrier wait is bounded (ptx.cuh); no TMA load uses cluster multicast.
+#include <type_traits>
+
 #include "common.cuh"
 #include "ptx.cuh"
 
@@ -69,6 +71,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   uint64_t* p_ready = bars + 11;        // [2] first half of P_q (keys 0-63) written
   uint64_t* p_ready_hi = bars + 16;     // [2] second half written
   uint64_t* o_done = bars + 13;         // [2]
+  uint64_t* turn = bars + 18;           // [2] hand-over of the exponential section between the two softmax groups
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 20);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
@@ -93,13 +96,14 @@ __global__ void __launch_bounds__(kThreads, 1)
     mbar_init(q_full, 1);
     for (int i = 0; i < 2; ++i) {
       mbar_init(&k_full[i], 1);
-      mbar_init(&k_empty[i], 1);
+      mbar_init(&k_empty[i], 2);  // one arrival per MMA-issuing thread
       mbar_init(&v_full[i], 1);
-      mbar_init(&v_empty[i], 1);
+      mbar_init(&v_empty[i], 2);
       mbar_init(&s_full[i], 1);
       mbar_init(&p_ready[i], 128);
       mbar_init(&p_ready_hi[i], 128);
       mbar_init(&o_done[i], 1);
+      mbar_init(&turn[i], 128);
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -156,92 +160,94 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
       }
     }
-  } else if (warp == kWarpMma) {
-    // ------------------------------------------------------------------ MMA issuer
+  } else if (warp == kWarpMma || warp == kWarpMma + 1) {
+    // ------------------------------------------------------------------ MMA issuers, one thread per query tile
+    // Each query tile has its own issuing thread (warps 9 and 10).  One thread for both tiles was the
+    // kernel's bottleneck: besides the 32 MMAs of a key tile it has a dozen barrier waits, fences and commits
+    // to execute, each a round trip of ~100 clocks for a single thread, and the two tiles' chains
+    // (S -> softmax -> P.V -> next S) queued behind each other in it.  tcgen05 operations of ONE thread execute
+    // in issue order, which is all the ordering a query tile needs (S_q(j+1) overwrites P_q(j) only after
+    // P_q(j).V(j) has read it); the two tiles share only the read-only K and V stages, which each thread
+    // releases with its own arrival (the empty barriers count two).
+    const int mq = warp - kWarpMma;
     if (lane == 0 && n_max > 0) {
       constexpr uint32_t idesc_s = umma_idesc_f16(BM, BN, BF16, false, false);
       constexpr uint32_t idesc_o = umma_idesc_f16(BM, D, BF16, false, true);
       const uint32_t sq = smem_u32(smem + L::kQ), sk = smem_u32(smem + L::kK), sv = smem_u32(smem + L::kV);
       bool ok = mbar_wait(q_full, 0, abort_flag, p.status, ST_ATTN_Q);
       tc_fence_after_sync();
-
-      // One thread issues every MMA, and a 128x128x16 MMA runs for only 64 clocks, so the
-      // instruction count per issue matters: descriptors are built once per tile and the k16
-      // slices only add a compile-time constant to the start-address field (low word).
-      const uint64_t dq0 = umma_desc_kmajor_sw128(sq), dq1 = umma_desc_kmajor_sw128(sq + L::kTileBytes);
-      const uint64_t dk0 = umma_desc_kmajor_sw128(sk), dk1 = umma_desc_kmajor_sw128(sk + L::kTileBytes);
-      const uint64_t dv0 = umma_desc_mnmajor_sw128(sv, kBoxBytes, 1024);
-      const uint64_t dv1 = umma_desc_mnmajor_sw128(sv + L::kTileBytes, kBoxBytes, 1024);
-      auto issue_s = [&](int q, int stage) {
-        const uint32_t d_tmem = tmem_base + q * 128;
-        const uint64_t da = q ? dq1 : dq0, db = stage ? dk1 : dk0;
-#pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint64_t off = static_cast<uint64_t>(((kk / 4) * kBoxBytes + (kk % 4) * 32) >> 4);
-          umma_f16_ss(d_tmem, da + off, db + off, idesc_s, kk != 0);
-        }
-        umma_commit(&s_full[q]);
-      };
-      int v_waited = 0;  // V tiles [0, v_waited) are known to have landed
-      auto ensure_v = [&](int j) {
-        while (ok && v_waited <= j) {
-          ok = mbar_wait(&v_full[v_waited % kStagesKV], (v_waited / kStagesKV) & 1, abort_flag, p.status,
-                         ST_ATTN_KV);
-          ++v_waited;
-        }
-        tc_fence_after_sync();
-      };
-
-      // O_q += P_q(j) . V(j).  The softmax group publishes P in two halves (64 keys each), so
-      // the first four k16 slices start while the second half is still being exponentiated.
-      int pass_index = 0;       // 0 for the first pass that runs, 1 for the second
-      bool stats_pass = false;  // the pass that only gathers statistics issues no P.V
-      auto issue_pv = [&](int q, int stage, int j) {
-        const uint32_t d_tmem = tmem_base + 256 + q * 128;
-        const uint32_t a_tmem = tmem_base + q * 128;  // P_q: 8 columns per k16 slice
-        const uint64_t dv = stage ? dv1 : dv0;
-        const uint32_t parity = (pass_index * nq[q] + j) & 1;
-#pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          // in the statistics pass this only learns that the softmax group is done with S_q
-          if (ok) ok = mbar_wait(half ? &p_ready_hi[q] : &p_ready[q], parity, abort_flag, p.status, ST_ATTN_P);
-          if (stats_pass) continue;
-          if (half == 0) ensure_v(j);
-          if (!ok) return;
-          tc_fence_after_sync();
-#pragma unroll
-          for (int kk = half * 4; kk < half * 4 + 4; ++kk)
-            umma_f16_ts(d_tmem, a_tmem + kk * 8, dv + static_cast<uint64_t>((kk * 2048) >> 4), idesc_o,
-                        (j | kk) != 0);
-        }
-        if (!stats_pass) umma_commit(&o_done[q]);
-      };
-
+      // descriptors are built once; the k16 slices only add a constant to the start-address field
+      const uint64_t dq = umma_desc_kmajor_sw128(sq + mq * L::kTileBytes);
+      const uint64_t dk[2] = {umma_desc_kmajor_sw128(sk), umma_desc_kmajor_sw128(sk + L::kTileBytes)};
+      const uint64_t dv[2] = {umma_desc_mnmajor_sw128(sv, kBoxBytes, 1024),
+                              umma_desc_mnmajor_sw128(sv + L::kTileBytes, kBoxBytes, 1024)};
+      const uint32_t t_sq = tmem_base + mq * 128;        // S_q; P_q aliases its first 64 columns (8 per k16 slice)
+      const uint32_t t_oq = tmem_base + 256 + mq * 128;  // O_q
+      const int n_mine = nq[mq];
+      int kt = 0, vt = 0;  // K / V tiles seen so far (ring positions; K is streamed once per pass)
+      int pass_index = 0;  // 0 for the first pass that runs, 1 for the second
       for (int pass = first_pass; pass < 2 && ok; ++pass, ++pass_index) {
-        stats_pass = pass == 0;
-        const int kbase = pass_index * n_max;  // K tiles consumed by the earlier pass
-        for (int j = 0; j < n_max && ok; ++j) {
-          const int stage = (kbase + j) % kStagesKV;  // K stage; V tiles only exist in the last pass: stage j % 2
-          ok = mbar_wait(&k_full[stage], ((kbase + j) / kStagesKV) & 1, abort_flag, p.status, ST_ATTN_KV);
+        const bool stats_pass = pass == 0;  // the pass that only gathers statistics issues no P.V
+        // Per key tile and query tile the dependent chain is: softmax publishes P(j) -> P(j).V(j) -> S(j+1) ->
+        // softmax.  Everything this thread can do off that chain is done off it: the wait for K(j+1) happens
+        // before the wait for P(j), and the commits that release V(j), K(j+1) and publish O come after the
+        // MMAs of S(j+1) have been issued (a commit covers everything issued before it, so they only fire a
+        // little later than strictly possible).
+        bool have_k = false;  // K(j) of the current pass is known to have landed
+        for (int j = 0; j < n_max && ok; ++j, ++kt) {
+          const int ks = kt % kStagesKV;
+          if (!have_k) ok = mbar_wait(&k_full[ks], (kt / kStagesKV) & 1, abort_flag, p.status, ST_ATTN_KV);
+          have_k = false;
           if (!ok) break;
-          tc_fence_after_sync();
-          if (j < nq[0]) issue_s(0, stage);
-          if (j >= 1 && j - 1 < nq[1]) {  // O1 += P1(j-1) . V(j-1)
-            issue_pv(1, (j - 1) % kStagesKV, j - 1);
-            if (!ok) break;
+          if (j < n_mine) {
+            tc_fence_after_sync();
+#pragma unroll
+            for (int kk = 0; kk < D / 16; ++kk) {
+              const uint64_t off = static_cast<uint64_t>(((kk / 4) * kBoxBytes + (kk % 4) * 32) >> 4);
+              umma_f16_ss(t_sq, dq + off, dk[ks] + off, idesc_s, kk != 0);
+            }
+            umma_commit(&s_full[mq]);
+            umma_commit(&k_empty[ks]);  // this tile's use of the K stage ends when these MMAs have read it
+            if (j > 0 && !stats_pass) {  // (deferred from the previous tile)
+              umma_commit(&o_done[mq]);
+              umma_commit(&v_empty[(vt - 1) % kStagesKV]);
+            }
+          } else {
+            mbar_arrive(&k_empty[ks]);  // a key tile only the other query tile needs
           }
-          if (j >= 1 && !stats_pass) umma_commit(&v_empty[(j - 1) % kStagesKV]);  // both P.V of tile j-1 are issued
-          if (j < nq[1]) issue_s(1, stage);
-          umma_commit(&k_empty[stage]);  // both S of tile j are issued
-          if (j < nq[0]) {               // O0 += P0(j) . V(j)
-            issue_pv(0, j % kStagesKV, j);
+          const int vs = vt % kStagesKV;
+          if (j < n_mine) {
+            // the next K tile, while the softmax group works on this one
+            if (j + 1 < n_max) {
+              ok = mbar_wait(&k_full[(kt + 1) % kStagesKV], ((kt + 1) / kStagesKV) & 1, abort_flag, p.status, ST_ATTN_KV);
+              have_k = ok;
+            }
+            if (!stats_pass && ok) ok = mbar_wait(&v_full[vs], (vt / kStagesKV) & 1, abort_flag, p.status, ST_ATTN_KV);
+            // O_q += P_q(j) . V(j).  The softmax group publishes P in two halves (64 keys each), so the first
+            // four k16 slices start while the second half is still being exponentiated.  In the statistics
+            // pass the two waits only tell that the softmax group is done with S_q.
+            const uint32_t parity = (pass_index * n_mine + j) & 1;
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+              if (ok) ok = mbar_wait(half ? &p_ready_hi[mq] : &p_ready[mq], parity, abort_flag, p.status, ST_ATTN_P);
+              if (stats_pass) continue;
+              if (!ok) break;
+              tc_fence_after_sync();
+#pragma unroll
+              for (int kk = half * 4; kk < half * 4 + 4; ++kk)
+                umma_f16_ts(t_oq, t_sq + kk * 8, dv[vs] + static_cast<uint64_t>((kk * 2048) >> 4), idesc_o,
+                            (j | kk) != 0);
+            }
             if (!ok) break;
+            if (!stats_pass && (j + 1 >= n_mine)) {  // no further S of this tile follows: publish now
+              umma_commit(&o_done[mq]);
+              umma_commit(&v_empty[vs]);
+            }
+          } else if (!stats_pass) {
+            ok = mbar_wait(&v_full[vs], (vt / kStagesKV) & 1, abort_flag, p.status, ST_ATTN_KV);
+            if (ok) mbar_arrive(&v_empty[vs]);
           }
-        }
-        if (ok && n_max >= 1) {
-          const int j = n_max - 1;
-          if (j < nq[1]) issue_pv(1, j % kStagesKV, j);
-          if (ok && !stats_pass) umma_commit(&v_empty[j % kStagesKV]);
+          if (!stats_pass) ++vt;
         }
       }
     }
@@ -340,16 +346,33 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
       l_sum = 1.0f;  // P is already normalised
     } else
-    for (int j = 0; j < n_tiles; ++j) {
-      if (!mbar_wait(&s_full[q], j & 1, abort_flag, p.status, ST_ATTN_S)) {
+    // The two softmax groups take turns: group 1 starts the arithmetic of its key tile j when group 0 has
+    // finished that of its tile j, and group 0 starts tile j+1 when group 1 has finished tile j.  Left alone the
+    // two groups fall into step (they share the K/V ring and the tensor pipe), exponentiate at the same time
+    // on the same four schedulers and then both sit idle while their MMAs run; taking turns, one group works
+    // alone (a third faster) while the other group's P.V and next S are in flight.  A group with fewer key
+    // tiles than the other keeps passing the turn on until the other is done.
+    for (int j = 0; j < n_max; ++j) {
+      const bool mine = j < n_tiles;
+      uint32_t sr[4][32];
+      if (mine) {
+        if (!mbar_wait(&s_full[q], j & 1, abort_flag, p.status, ST_ATTN_S)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+#pragma unroll
+        for (int c = 0; c < 4; ++c) tmem_ld_32x32b_x32(t_s + c * 32, sr[c]);
+        tmem_ld_wait();
+      }
+      if (!mbar_wait(&turn[q], q == 0 ? ((j & 1) ^ 1) : (j & 1), abort_flag, p.status, ST_ATTN_S)) {
         ok = false;
         break;
       }
-      tc_fence_after_sync();
-      uint32_t sr[4][32];
-#pragma unroll
-      for (int c = 0; c < 4; ++c) tmem_ld_32x32b_x32(t_s + c * 32, sr[c]);
-      tmem_ld_wait();
+      if (!mine) {
+        mbar_arrive(&turn[q ^ 1]);
+        continue;
+      }
 
       const int n0 = j * BN;
       const bool needs_mask = (n0 + BN > p.S_kv) || (p.causal && (n0 + BN - 1 > m_tile + off));
@@ -363,28 +386,57 @@ __global__ void __launch_bounds__(kThreads, 1)
           for (int i = 0; i < 32; ++i)
             if (c * 32 + i > limit) sr[c][i] = 0xff800000u;  // -inf
       }
-      // row maximum: four independent chains of three-input max
-      float mxc[4];
+      // P = 2^(s*scale_log2 - m_ref) with packed fp32 FMAs, row sum in fp32, P rounded to 16 bits.
+      // Two 32-key chunks at a time, interleaved pair by pair so that the special-function unit always has
+      // independent work.  WITH_MAX also runs the row maximum of all 128 keys (four chains of three-input
+      // max, two keys of every chunk per step) through the same loop: the maximum is a chain on the ALU, the
+      // exponentials are bound by the special-function unit, and neither waits for the other.
+      const float2 scale2 = make_float2(p.scale_log2, p.scale_log2);
+      float mxc[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+      auto exp_chunks = [&](int c0, float mref, uint32_t (&pa)[16], uint32_t (&pb)[16], float2& sum, auto with_max) {
+        const float2 negm2 = make_float2(-mref, -mref);
+        float2 sa = make_float2(0.f, 0.f), sb = make_float2(0.f, 0.f);
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        mxc[c] = max3f(__uint_as_float(sr[c][0]), __uint_as_float(sr[c][1]), __uint_as_float(sr[c][2]));
+        for (int i = 0; i < 16; ++i) {
+          const float2 xa = fma2(make_float2(__uint_as_float(sr[c0][2 * i]), __uint_as_float(sr[c0][2 * i + 1])), scale2, negm2);
+          const float2 xb = fma2(make_float2(__uint_as_float(sr[c0 + 1][2 * i]), __uint_as_float(sr[c0 + 1][2 * i + 1])), scale2, negm2);
+          if (decltype(with_max)::value) {
 #pragma unroll
-        for (int i = 3; i + 1 < 32; i += 2)
-          mxc[c] = max3f(mxc[c], __uint_as_float(sr[c][i]), __uint_as_float(sr[c][i + 1]));
-        mxc[c] = fmaxf(mxc[c], __uint_as_float(sr[c][31]));
-      }
+            for (int c = 0; c < 4; ++c)
+              mxc[c] = max3f(mxc[c], __uint_as_float(sr[c][2 * i]), __uint_as_float(sr[c][2 * i + 1]));
+          }
+          const float2 ea = make_float2(ex2f(xa.x), ex2f(xa.y));
+          const float2 eb = make_float2(ex2f(xb.x), ex2f(xb.y));
+          sa = add2(sa, ea);
+          sb = add2(sb, eb);
+          pa[i] = pack16<BF16>(ea.x, ea.y);
+          pb[i] = pack16<BF16>(eb.x, eb.y);
+        }
+        sum = add2(sa, sb);
+      };
+
+      // Optimistic first half: the exponentials of keys 0-63 are taken relative to the reference maximum
+      // the row already has, so they do not wait for the row maximum.  Only when the maximum turns out to
+      // have grown by more than the threshold (rare after the first tiles; always on the first tile, whose
+      // reference is -infinity) is O rescaled and the half recomputed.  The stale reference cannot overflow
+      // what is kept: a value that would exceed 2^threshold is by construction one that triggers the
+      // recomputation.
+      uint32_t pk0[16], pk1[16];
+      float2 sum01;
+      exp_chunks(0, m_ref, pk0, pk1, sum01, std::true_type());
       const float mx = max3f(mxc[0], mxc[1], fmaxf(mxc[2], mxc[3]));
       float m_new = fmaxf(m_ref, mx * p.scale_log2);
       if (m_new == -INFINITY) m_new = 0.f;  // a row that sees no key yet: keep everything finite
-
       // lazy rescale: warp-uniform decision because the TMEM accesses are warp-collective
       const bool grow = (j > 0) && (m_new - m_ref > kRescaleThreshold);
+      bool redo = j == 0;
       if (j == 0) {
         m_ref = m_new;
       } else if (__any_sync(0xffffffffu, grow)) {
         const float factor = ex2f(m_ref - m_new);
         m_ref = m_new;
         l_sum *= factor;
+        redo = true;
         // O_q must be complete up to tile j-1 before it is scaled
         if (!mbar_wait(&o_done[q], (j - 1) & 1, abort_flag, p.status, ST_ATTN_O)) {
           ok = false;
@@ -401,31 +453,23 @@ __global__ void __launch_bounds__(kThreads, 1)
           tmem_st_32x32b_x32(t_o + c * 32, o);
         }
       }
-
-      // P = 2^(s*scale_log2 - m_ref) with packed fp32 FMAs, row sum in fp32 (two packed
-      // accumulators), P rounded to 16 bits and written back over S chunk by chunk
-      const float2 scale2 = make_float2(p.scale_log2, p.scale_log2);
-      const float2 negm2 = make_float2(-m_ref, -m_ref);
-      float2 sum_a = make_float2(0.f, 0.f), sum_b = make_float2(0.f, 0.f);
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t pk[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          float2 x = fma2(make_float2(__uint_as_float(sr[c][2 * i]), __uint_as_float(sr[c][2 * i + 1])), scale2, negm2);
-          float2 e = make_float2(ex2f(x.x), ex2f(x.y));
-          if (i & 1) sum_b = add2(sum_b, e); else sum_a = add2(sum_a, e);
-          pk[i] = pack16<BF16>(e.x, e.y);
-        }
-        tmem_st_32x32b_x16(t_s + c * 16, pk);
-        if (c & 1) {  // a half of P (64 keys) is complete: let the MMA warp start on it
-          tmem_st_wait();
-          tc_fence_before_sync();
-          mbar_arrive(c == 1 ? &p_ready[q] : &p_ready_hi[q]);
-        }
-      }
-      sum_a = add2(sum_a, sum_b);
-      l_sum += sum_a.x + sum_a.y;
+      if (redo) exp_chunks(0, m_ref, pk0, pk1, sum01, std::false_type());
+      // P is written back over S chunk by chunk; a half of P (64 keys) that is complete lets the MMA warp start on it
+      tmem_st_32x32b_x16(t_s, pk0);
+      tmem_st_32x32b_x16(t_s + 16, pk1);
+      tmem_st_wait();
+      tc_fence_before_sync();
+      mbar_arrive(&p_ready[q]);
+      float2 sum23;
+      exp_chunks(2, m_ref, pk0, pk1, sum23, std::false_type());
+      tmem_st_32x32b_x16(t_s + 32, pk0);
+      tmem_st_32x32b_x16(t_s + 48, pk1);
+      tmem_st_wait();
+      tc_fence_before_sync();
+      mbar_arrive(&p_ready_hi[q]);
+      mbar_arrive(&turn[q ^ 1]);
+      const float2 tot = add2(sum01, sum23);
+      l_sum += tot.x + tot.y;
     }
 
     // ---- epilogue: O / l
