@@ -460,6 +460,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       tmem_st_wait();
       tc_fence_before_sync();
       mbar_arrive(&p_ready[q]);
+      mbar_arrive(&turn[q ^ 1]);  // the other group may start while this one finishes keys 64-127
       float2 sum23;
       exp_chunks(2, m_ref, pk0, pk1, sum23, std::false_type());
       tmem_st_32x32b_x16(t_s + 32, pk0);
@@ -467,7 +468,6 @@ __global__ void __launch_bounds__(kThreads, 1)
       tmem_st_wait();
       tc_fence_before_sync();
       mbar_arrive(&p_ready_hi[q]);
-      mbar_arrive(&turn[q ^ 1]);
       const float2 tot = add2(sum01, sum23);
       l_sum += tot.x + tot.y;
     }
