@@ -19,10 +19,11 @@ enum : unsigned { ST_ATTN_S = 0x201, ST_ATTN_P = 0x202, ST_ATTN_O = 0x203, ST_AT
 struct AttnParams {
   int S_q, S_kv, n_pairs, causal;
   int normalized;  // 1: two passes over the keys, P divided by the complete row sum before it is rounded
-  int64_t total_ctas;
+  int64_t total_items;  // work items: pairs of 128-row query tiles of one (batch, head)
   float scale_log2, scale;
   void* O;
   unsigned* status;
+  unsigned* work;  // [0] next work item, [1] CTAs that have finished; both zero between launches
 };
 
 __device__ __forceinline__ float ex2f(float x) {
