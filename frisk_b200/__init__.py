@@ -5,7 +5,7 @@ attention path (``python/frisk/__init__.py:1-4``): the builder classes of
 ``frisk_ffi.ir`` and the ``FriskHelper`` conveniences, plus ``execute`` /
 ``attention_forward``, which run on the GPU through ``libfrisk_b200``.
 """
-from . import capi, ir
+from . import capi, ir, tensor_ops
 from .execute import attention_forward, attention_geometry, execute, fused_plan, gemm, gemm_plan
 from .helper import FriskHelper, create_context, create_session
 from .affine import (AffineBinaryOpExpr, AffineConstantExpr, AffineDimExpr, AffineExpr, AffineExprKind,
@@ -13,6 +13,9 @@ from .affine import (AffineBinaryOpExpr, AffineConstantExpr, AffineDimExpr, Affi
                      get_affine_dim_expr, get_affine_symbol_expr)
 from .ir import (AffineMap, AllocBufferOp, BlockOp, CopyOp, FillOp, ForOp, GemmOp, GemmWarpPolicy, KernelOp,
                  MemorySpace, OpState, ParallelOp, ReduceOp, block, builder, context, frisk, module, type, value)
+
+from .tensor_ops import (AttentionBuilder, LayoutViewOp, MmaOp, ReduceTensorOp, TileLoadOp, TileStoreOp, attention_plan,
+                         build_attention_kernel)
 
 GLOBAL, SHARED, LOCAL = MemorySpace.GLOBAL, MemorySpace.SHARED, MemorySpace.LOCAL
 

@@ -11,14 +11,19 @@ pattern-matched on the host and dispatched through the C ABI of ``libfrisk_b200`
   (tile shapes there are scheduling hints; the hand-written kernels fix their own),
   optionally with a ``frisk.fill`` of C before it and a ``frisk.reduce`` of C along dim 1
   after it, which run inside the GEMM's epilogue;
-* the attention-forward graph, entered through :func:`attention_forward` with the
+* a kernel that holds the attention graph of
+  ``test/Transforms/attention-layout-tile-d64.mlir:23-63`` over ``frisk.mma`` /
+  ``frisk.reduce_tensor`` (``tensor_ops.attention_plan``): one [N_q, D] query tile over N_kv keys,
+  run by the attention kernel in its normalised mode (the graph divides by the complete row sum
+  before it rounds the probabilities);
+* the batched attention forward, entered through :func:`attention_forward` with the
   launch contract of ``tiled_attention.py:28-61`` (compact BHSD, spec dict B/H/N/D).
 
 Device memory, streams and process groups come from torch; the arithmetic does not.
 """
 import math
 
-from . import capi, ir
+from . import capi, ir, tensor_ops
 
 _TORCH_DTYPE = None
 
@@ -170,7 +175,11 @@ def execute(module_or_kernel, *tensors, stream=None, name=None, algo=capi.ALGO_A
     """Run the kernel on CUDA tensors bound positionally to its memref arguments."""
     torch = _torch()
     kernel = _kernel_of(module_or_kernel, name)
-    desc, (ia, ib, ic), epilogue = fused_plan(kernel, algo=algo)
+    attention = any(isinstance(op, tensor_ops.MmaOp) for op in tensor_ops._ops_of(kernel))
+    if attention:
+        spec, arg_idx = tensor_ops.attention_plan(kernel)
+    else:
+        desc, (ia, ib, ic), epilogue = fused_plan(kernel, algo=algo)
     arg_types = kernel.attrs["function_type"].inputs
     if len(tensors) != len(arg_types):
         raise ValueError(f"frisk-b200-execute: kernel takes {len(arg_types)} tensors, got {len(tensors)}")
@@ -184,6 +193,14 @@ def execute(module_or_kernel, *tensors, stream=None, name=None, algo=capi.ALGO_A
         want = {"f16": torch.float16, "bf16": torch.bfloat16, "f32": torch.float32}.get(ty.element.name)
         if t.dtype != want:
             raise ValueError(f"frisk-b200-execute: tensor dtype {t.dtype} does not match {ty}")
+    if attention:
+        q, k, v, o = (tensors[i] for i in arg_idx)
+        adesc = capi.attn_desc(1, 1, spec["S_q"], spec["S_kv"], spec["D"], spec["scale"], False, spec["dtype_in"],
+                               spec["dtype_out"], normalize_p=True)
+        ctx = context_for(o.device.index or 0)
+        ctx.attention_fwd(adesc, q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),
+                          stream=_stream_ptr(stream, o.device))
+        return o
     a, b, c = tensors[ia], tensors[ib], tensors[ic]
     dev = c.device.index or 0
     ctx = context_for(dev)

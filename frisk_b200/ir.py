@@ -729,6 +729,8 @@ def _verify(op):
                                  f"destination[{j}] = {dst.shape[j]}")
         if src.element != dst.element:
             raise ValueError("source and destination must have the same element type")
+    elif hasattr(op, "verify_op"):  # the tensor-level ops (tensor_ops.py) carry their own verifiers
+        op.verify_op()
     elif isinstance(op, CopyOp):  # FriskOps.cpp:662-679
         if len(op.get_src_indices()) != op.attrs["srcMap"].get_num_inputs():
             raise ValueError("source index count does not match the source map")
@@ -859,4 +861,6 @@ class _Printer:
             return [f"{pad}frisk.gemm({ops})" + _attr_dict(op.attrs) + f" : {tys}"]
         if isinstance(op, EndOp):
             return [pad + "frisk.end"]
+        if hasattr(op, "print_assembly"):
+            return [pad + op.print_assembly(n)]
         return [pad + f'"{op.op_name}"()' + _attr_dict(op.attrs)]

@@ -249,3 +249,42 @@ def test_launch_contract_refusals(ctx):
     # inputs may alias each other
     ctx.attention_fwd(desc, q.data_ptr(), q.data_ptr(), q.data_ptr(), o.data_ptr(), stream=s)
     ctx.check(s)
+
+
+def test_attention_graph_built_with_the_ir_and_executed(ctx):
+    """The attention graph of test/Transforms/attention-layout-tile-d64.mlir:23-63, built over frisk.mma /
+    frisk.reduce_tensor and run through F.execute: on the reference's own fixtures (one 64 x 64 head at a time,
+    D = 64, scale 0.125, fp16 in, fp32 out) the analytic ones come out bit for bit, all inside its checker's bounds."""
+    import torch
+
+    import frisk_b200 as F
+    from tests.test_frontend import build_attention_module
+    from tests.util import to_device
+    module, _ = build_attention_module(64, 64, 64, "f16", 0x3E000000, "f32")
+    g = np.load(GOLDEN / "attention_tiled_d64.npz")
+    for name in ("random", "uniform-sparse-value", "last-key-dominant", "tail-uniform", "key-boundary"):
+        key = f"{name}/n64"
+        q, k, v = g[key + "/q"], g[key + "/k"], g[key + "/v"]
+        for b in range(q.shape[0]):
+            for h in range(q.shape[1]):
+                tq, tk, tv = (to_device(x[b, h], "fp16") for x in (q, k, v))
+                to = torch.full((64, 64), float("nan"), dtype=torch.float32, device="cuda")
+                F.execute(module, tq, tk, tv, to)
+                torch.cuda.synchronize()
+                got = to.cpu().numpy()
+                assert np.isfinite(got).all()
+                assert ao.within_reference_tolerance(got, g[key + "/strict"][b, h], "strict") <= 1.0, key
+                if name != "random" and name != "key-boundary":
+                    assert np.array_equal(got.view(np.uint32), g[key + "/strict"][b, h].view(np.uint32)), key
+    # a larger tile of the benchmark's head shape, bf16 in and out, against the strict oracle
+    module, _ = build_attention_module(256, 512, 128, "bf16", 128 ** -0.5, "bf16")
+    rng = np.random.default_rng(21)
+    from oracle.numerics import to_storage
+    q = to_storage(rng.standard_normal((1, 1, 256, 128), dtype=np.float32), "bf16")
+    k, v = (to_storage(rng.standard_normal((1, 1, 512, 128), dtype=np.float32), "bf16") for _ in range(2))
+    tq, tk, tv = (to_device(x[0, 0], "bf16") for x in (q, k, v))
+    to = torch.empty(256, 128, dtype=torch.bfloat16, device="cuda")
+    F.execute(module, tq, tk, tv, to)
+    torch.cuda.synchronize()
+    ref = ao.attention_fwd(q, k, v, "bf16", 128 ** -0.5, causal=False, mode="strict")[0, 0]
+    assert rel_frobenius(to.float().cpu().numpy(), ref) <= 5e-3

@@ -304,3 +304,82 @@ def test_affine_expressions_simplify_and_print_like_the_reference_binding():
     assert F.AffineMap.get_permutation_map([1, 0], None).is_permutation()
     assert not F.AffineMap() and str(F.AffineMap()) == "<<NULL AFFINE MAP>>" and F.AffineMap.get(None).is_empty()
     assert F.AffineMap.get_constant_map(5, None).get_single_constant_result() == 5
+
+
+# ------------------------------------------------------------------ the attention graph over frisk.mma
+def build_attention_module(n_q=64, n_kv=64, d=64, dtype="f16", scale=0x3E000000, out="f32"):
+    context = F.context()
+    F.frisk.load_dialects(context)
+    builder = F.builder(context)
+    module = builder.create_module()
+    module.context = context
+    el = {"f16": builder.get_f16_ty, "bf16": builder.get_bf16_ty, "f32": builder.get_f32_ty}
+    kernel = F.build_attention_kernel(builder, module, "attention_q64_full_kv", n_q, n_kv, d, el[dtype](), scale, el[out]())
+    return module, kernel
+
+
+def test_attention_graph_prints_the_reference_assembly():
+    """The op lines of test/Transforms/attention-layout-tile-d64.mlir:44-61 in the ops' declared assembly formats
+    (include/Dialect/Frisk/IR/FriskLayoutOps.td: reduce_tensor :29, mma :47, layout_view :73, tile_store :97)."""
+    module, kernel = build_attention_module()
+    assert module.verify()
+    text = str(module)
+    for line in (
+        "frisk.kernel @attention_q64_full_kv(memref<64x64xf16, 1>, memref<64x64xf16, 1>, memref<64x64xf16, 1>, memref<64x64xf32, 1>) {",
+        "= memref.alloc() {alignment = 1024 : i64} : memref<64x64xf16, 3>",
+        "frisk.parallel (%arg4) = (1), threads = 128 {",
+        "= frisk.layout_view %arg0 : memref<64x64xf16, 1> -> memref<64x64xf16, 1>",
+        "= arith.constant dense<0.0> : tensor<64x64xf32>",
+        "{k = 64 : i64, m = 64 : i64, n = 64 : i64, trans_b = true} : memref<64x64xf16, 3>, memref<64x64xf16, 3>, tensor<64x64xf32> -> tensor<64x64xf32>",
+        "= arith.constant dense<0x3E000000> : tensor<64x64xf32>",
+        '{dim = 1 : i64, kind = "max"} : tensor<64x64xf32> -> tensor<64xf32>',
+        "outs(%14 : tensor<64x64xf32>) dimensions = [1]",
+        '{dim = 1 : i64, kind = "sum"} : tensor<64x64xf32> -> tensor<64xf32>',
+        "= arith.truncf %21 : tensor<64x64xf32> to tensor<64x64xf16>",
+        "{k = 64 : i64, m = 64 : i64, n = 64 : i64} : tensor<64x64xf16>, memref<64x64xf16, 3>, tensor<64x64xf32> -> tensor<64x64xf32>",
+        "frisk.tile_store %24, %25 : tensor<64x64xf32>, memref<64x64xf32, 1>",
+    ):
+        assert line in text, line
+
+
+def test_attention_plan_resolves_the_graph():
+    _, kernel = build_attention_module()
+    spec, idx = F.attention_plan(kernel)
+    assert spec == dict(S_q=64, S_kv=64, D=64, scale=0.125, dtype_in="fp16", dtype_out="fp32") and idx == (0, 1, 2, 3)
+    _, kernel = build_attention_module(128, 512, 128, "bf16", 128 ** -0.5, "bf16")
+    spec, _ = F.attention_plan(kernel)
+    assert (spec["S_q"], spec["S_kv"], spec["D"], spec["dtype_in"], spec["dtype_out"]) == (128, 512, 128, "bf16", "bf16")
+    assert abs(spec["scale"] - 128 ** -0.5) < 1e-7
+    with pytest.raises(ValueError, match="head dimension"):
+        F.attention_plan(build_attention_module(64, 64, 32)[1])
+    import torch
+    t = torch.zeros(64, 64, dtype=torch.float16)
+    with pytest.raises(ValueError, match="no CPU path"):
+        F.execute(build_attention_module()[0], t, t, t, torch.zeros(64, 64))
+
+
+def test_tensor_op_verifiers_reject_what_the_reference_rejects():
+    """MmaOp::verify, ReduceTensorOp::verify, TileStoreOp::verify (lib/Dialect/Frisk/IR/FriskLayoutOps.cpp:33-66,78-119,229-245)."""
+    b = F.builder(F.context())
+    ab = F.AttentionBuilder(b)
+    f16, f32 = b.get_f16_ty(), b.get_f32_ty()
+    shared = lambda shape, el=f16: ab.memref_alloc(el, shape).results[0]  # noqa: E731
+    zero = lambda shape, el=f32: ab.constant(ab.tensor_ty(el, shape), 0.0).results[0]  # noqa: E731
+    with pytest.raises(ValueError, match="mma-shape: matrix extents disagree with m/n/k and transpose"):
+        ab.mma(shared([64, 64]), shared([32, 64]), zero([64, 64]))          # B is [k, n]: k = 32 != 64
+    with pytest.raises(ValueError, match="mma-shape: incompatible input/accumulator element types"):
+        ab.mma(shared([64, 64], f32), shared([64, 64], f32), zero([64, 64], f16))
+    with pytest.raises(ValueError, match="mma-shape: incompatible input/accumulator element types"):
+        ab.mma(shared([64, 64]), shared([64, 64], b.get_bf16_ty()), zero([64, 64]))
+    with pytest.raises(ValueError, match="mma-shape: requires positive static rank-2 floating matrices"):
+        ab.mma(shared([64, 64, 2]), shared([64, 64]), zero([64, 64]))
+    ok = ab.mma(shared([64, 16]), shared([64, 16]), zero([64, 64]), trans_b=True)
+    assert (ok.attrs["m"], ok.attrs["n"], ok.attrs["k"]) == (64, 64, 16)
+    with pytest.raises(ValueError, match="reduce-shape: kind must be sum/max/min"):
+        ab.reduce_tensor(zero([64, 64]), "add", 1)
+    with pytest.raises(ValueError, match="reduce-shape: rank >= 2 and valid axis required"):
+        ab.reduce_tensor(zero([64, 64]), "max", 2)
+    with pytest.raises(ValueError, match="reduce-shape: requires static positive power-of-two extents"):
+        ab.reduce_tensor(zero([64, 96]), "max", 1)
+    with pytest.raises(ValueError, match="identical static shape and element type"):
+        ab.tile_store(zero([64, 64]), shared([64, 64]))                    # f32 tensor into an f16 memref
