@@ -5,7 +5,7 @@ attention path (``python/frisk/__init__.py:1-4``): the builder classes of
 ``frisk_ffi.ir`` and the ``FriskHelper`` conveniences, plus ``execute`` /
 ``attention_forward``, which run on the GPU through ``libfrisk_b200``.
 """
-from . import capi, ir, tensor_ops
+from . import capi, ir, packet, tensor_ops
 from .execute import attention_forward, attention_geometry, execute, fused_plan, gemm, gemm_plan
 from .helper import FriskHelper, create_context, create_session
 from .affine import (AffineBinaryOpExpr, AffineConstantExpr, AffineDimExpr, AffineExpr, AffineExprKind,

@@ -288,3 +288,25 @@ def test_attention_graph_built_with_the_ir_and_executed(ctx):
     torch.cuda.synchronize()
     ref = ao.attention_fwd(q, k, v, "bf16", 128 ** -0.5, causal=False, mode="strict")[0, 0]
     assert rel_frobenius(to.float().cpu().numpy(), ref) <= 5e-3
+
+
+def test_execution_packet_runs_on_the_attention_kernel(ctx):
+    """A packet in the export pass's schema (lib/Conversion/FriskLayoutToGPU/ExportExecution.cpp:46-296), read back
+    and executed: the same bits as the graph built directly."""
+    import torch
+
+    import frisk_b200 as F
+    from tests.test_frontend import build_attention_module
+    from tests.util import to_device
+    module, _ = build_attention_module(64, 64, 64, "f16", 0x3E000000, "f32")
+    pk = F.packet.export(module)
+    g = np.load(GOLDEN / "attention_tiled_d64.npz")
+    key = "last-key-dominant/n64"
+    tq, tk, tv = (to_device(g[key + "/" + n][0, 1], "fp16") for n in "qkv")
+    a = torch.full((64, 64), float("nan"), dtype=torch.float32, device="cuda")
+    b = torch.full((64, 64), float("nan"), dtype=torch.float32, device="cuda")
+    F.execute(module, tq, tk, tv, a)
+    F.packet.execute(pk, tq, tk, tv, b)
+    torch.cuda.synchronize()
+    assert torch.equal(a, b)
+    assert np.array_equal(b.cpu().numpy().view(np.uint32), g[key + "/strict"][0, 1].view(np.uint32))
