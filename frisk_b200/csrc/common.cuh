@@ -73,7 +73,7 @@ struct frisk_b200_ctx {
   unsigned* d_status = nullptr;  // device status word (first failing wait records its code)
   unsigned* h_status = nullptr;  // pinned mirror
   // staging for the *_host entry points and library-owned workspace
-  fb::StagingBuffer stage[7];  // 0-2 A/B/C staging, 3 skinny scratch, 4 V staging, 5 GEMM tail scratch, 6 row partials
+  fb::StagingBuffer stage[8];  // 0-2 A/B/C staging, 3 skinny scratch, 4 V staging, 5 GEMM tail scratch, 6 row partials, 7 fp32 stream-K scratch
   cudaStream_t host_stream = nullptr;
   cudaStream_t copy_stream = nullptr;
   cudaStream_t out_stream = nullptr;

@@ -17,6 +17,12 @@
  * synchronise, except the *_host entry points, which return after the result is in host
  * memory.  Inputs are read-only and may alias each other; the output must not overlap an
  * input (benchmark/layout/execution/tiled_execution.py:113-139).
+ *
+ * One context serves one stream of calls: the context holds scratch that its kernels share
+ * (the attention kernel's work counter, the fp32 and skinny GEMMs' tickets and partial sums when
+ * no workspace is passed, the device status word), so two calls on the same context must not
+ * run on the GPU at the same time.  Use one context per concurrent stream.  Every entry point
+ * leaves the calling thread's current device as it found it.
  */
 #ifndef FRISK_B200_H
 #define FRISK_B200_H
@@ -206,7 +212,8 @@ int frisk_b200_gemm_push(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc* desc, 
  * include/Dialect/Frisk/IR/FriskOps.td:400-423 and 425-453, reduce contract
  * lib/Dialect/Frisk/IR/FriskOps.cpp:728-762; the flow of test/python/bind_test.py:44-53).
  * frisk_b200_gemm_fused computes
- *     C <- (fill_enable ? fill_value : clear_accum ? 0 : C) + op(A).op(B)
+ *     C <- (clear_accum ? 0 : fill_enable ? fill_value : C) + op(A).op(B)
+ * (a fill before a gemm that overwrites C is dead: clear_accum wins)
  *     reduce_dst[i] <- (reduce_clear ? identity : reduce_dst[i]) (+) reduce_j C[i][j]
  * with the reduction taken over the values of C as stored (rounded to its element type) and
  * accumulated in fp32.  On the tcgen05 pair kernel both happen in the GEMM's epilogue (C is
