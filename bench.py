@@ -2,7 +2,7 @@
 """Benchmark of the GEMM / attention hot path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-    python bench.py --case tcgen05|skinny|simt|attention [--launches L]   (one kernel alone, for profilers)
+    python bench.py --case tcgen05|skinny|simt|f32|attention [--launches L]   (one kernel alone, for profilers)
 
 Prints ONE JSON line.  The headline workload is the fp16 GEMM M=N=K=4096, A row-major,
 B column-major (NT), fp32 accumulation, fp16 output, on the tcgen05 kernel.  A "step" is
@@ -609,28 +609,32 @@ def secondary(ctx, torch, stream, peaks, args, sampler, headline_sets, headline_
         ctx.check(stream)
         return total / (n or steps)
 
-    # fp32 GEMM 1024^3 (12 MiB of operands: rotate enough sets to stay ahead of L2)
-    try:
-        M = 1024
-        g = torch.Generator(device="cuda")
-        g.manual_seed(0)
-        sets = []
-        for _ in range(32):
-            a, b = (torch.rand(M, M, device="cuda", generator=g) * 2 - 1 for _ in range(2))
-            sets.append((a, b, torch.empty(M, M, device="cuda")))
-        desc = capi.gemm_desc(M, M, M, "fp32", "fp32")
-        ms = timed(lambda i: ctx.gemm(desc, *(t.data_ptr() for t in sets[i % len(sets)]), stream=stream), 20)
-        a, b, c = sets[0]
-        ctx.gemm(desc, a.data_ptr(), b.data_ptr(), c.data_ptr(), stream=stream)
-        torch.cuda.synchronize()
-        from oracle.numerics import rel_frobenius
-        err = rel_frobenius(c.double().cpu().numpy(), a.double().cpu().numpy() @ b.double().cpu().numpy())
-        res["gemm_f32_1024"] = {"ms": round(ms, 5), "tflops": round(2.0 * M ** 3 / ms / 1e9, 2),
-                                "frac_of_nominal_fp32_simt": round(2.0 * M ** 3 / ms / 1e9 / 80.0, 4),
-                                "err": float(f"{err:.3e}"), "checked": err <= 1e-3}
-        del sets
-    except Exception as e:  # noqa: BLE001
-        res["gemm_f32_1024"] = {"error": str(e)}
+    # fp32 GEMM 1024^3 (12 MiB of operands: rotate enough sets to stay ahead of L2), by both of its kernels:
+    # the default (operands split exactly into bf16 terms, nine tensor-core products) and the CUDA cores
+    for key, algo in (("gemm_f32_1024", capi.ALGO_AUTO), ("gemm_f32_1024_cuda_cores", capi.ALGO_SIMT_F32)):
+        try:
+            M = 1024
+            g = torch.Generator(device="cuda")
+            g.manual_seed(0)
+            sets = []
+            for _ in range(32):
+                a, b = (torch.rand(M, M, device="cuda", generator=g) * 2 - 1 for _ in range(2))
+                sets.append((a, b, torch.empty(M, M, device="cuda")))
+            desc = capi.gemm_desc(M, M, M, "fp32", "fp32", algo=algo)
+            ms = timed(lambda i: ctx.gemm(desc, *(t.data_ptr() for t in sets[i % len(sets)]), stream=stream), 40)
+            a, b, c = sets[0]
+            ctx.gemm(desc, a.data_ptr(), b.data_ptr(), c.data_ptr(), stream=stream)
+            torch.cuda.synchronize()
+            from oracle.numerics import rel_frobenius
+            err = rel_frobenius(c.double().cpu().numpy(), a.double().cpu().numpy() @ b.double().cpu().numpy())
+            res[key] = {"ms": round(ms, 5), "tflops": round(2.0 * M ** 3 / ms / 1e9, 2),
+                        "algo": {capi.ALGO_F32_SPLIT: "split_bf16x9_tcgen05", capi.ALGO_SIMT_F32: "cuda_cores"}[
+                            capi.load().frisk_b200_gemm_select(desc)],
+                        "frac_of_nominal_fp32_simt": round(2.0 * M ** 3 / ms / 1e9 / 80.0, 4),
+                        "err": float(f"{err:.3e}"), "checked": err <= 1e-3}
+            del sets
+        except Exception as e:  # noqa: BLE001
+            res[key] = {"error": str(e)}
     # skinny bf16 16 x 28672 x 8192 (470 MB of weights: larger than L2 by itself)
     try:
         M, N, K = 16, 28672, 8192
@@ -801,7 +805,7 @@ def run_case(args):
     torch.cuda.set_device(0)
     ctx = capi.Context(0)
     stream = torch.cuda.current_stream().cuda_stream
-    if args.case in ("tcgen05", "skinny", "simt"):
+    if args.case in ("tcgen05", "skinny", "simt", "f32"):
         if args.case == "tcgen05":
             M, N, K = args.m or 8192, args.n or 4096, args.k or 4096
             a = device_normal(torch, (M, K), torch.float16, 1 / math.sqrt(K), 1)
@@ -821,7 +825,9 @@ def run_case(args):
             a = torch.rand(M, K, device="cuda") * 2 - 1
             b = torch.rand(K, N, device="cuda") * 2 - 1
             c = torch.empty(M, N, device="cuda")
-            desc = capi.gemm_desc(M, N, K, "fp32", "fp32")
+            # simt: the CUDA-core kernel; f32: whatever AUTO picks (the split-bf16 tensor-core path at this size)
+            desc = capi.gemm_desc(M, N, K, "fp32", "fp32",
+                                  algo=capi.ALGO_SIMT_F32 if args.case == "simt" else capi.ALGO_AUTO)
             work, unit = 2.0 * M * N * K / 1e12, "TFLOP"
         fn = lambda: ctx.gemm(desc, a.data_ptr(), b.data_ptr(), c.data_ptr(), stream=stream)  # noqa: E731
     else:
@@ -853,7 +859,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-secondary", action="store_true", help="skip the informational extra workloads")
-    ap.add_argument("--case", choices=["tcgen05", "skinny", "simt", "attention"],
+    ap.add_argument("--case", choices=["tcgen05", "skinny", "simt", "f32", "attention"],
                     help="run ONE kernel on a profiling-sized problem instead of the benchmark")
     ap.add_argument("--launches", type=int, default=4)
     ap.add_argument("--m", type=int, default=0)

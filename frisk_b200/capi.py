@@ -11,7 +11,7 @@ import os
 import pathlib
 
 F32, F16, BF16 = 0, 1, 2
-ALGO_AUTO, ALGO_SIMT_F32, ALGO_TCGEN05, ALGO_SKINNY, ALGO_TCGEN05_PAIR = 0, 1, 2, 3, 4
+ALGO_AUTO, ALGO_SIMT_F32, ALGO_TCGEN05, ALGO_SKINNY, ALGO_TCGEN05_PAIR, ALGO_F32_SPLIT = 0, 1, 2, 3, 4, 5
 DTYPE_CODE = {"fp32": F32, "fp16": F16, "bf16": BF16}
 DTYPE_NAME = {v: k for k, v in DTYPE_CODE.items()}
 ITEMSIZE = {F32: 4, F16: 2, BF16: 2}

@@ -312,7 +312,7 @@ int frisk_b200_gemm_validate(const frisk_b200_gemm_desc* d) {
   GemmDims g = resolve_dims(*d);
   int64_t a_cols = d->trans_a ? g.M : g.K, b_cols = d->trans_b ? g.K : g.N;
   if (g.lda < a_cols || g.ldb < b_cols || g.ldc < g.N) return FRISK_B200_E_GEMM_SHAPE;
-  if (d->algo < FRISK_B200_ALGO_AUTO || d->algo > FRISK_B200_ALGO_TCGEN05_PAIR) return FRISK_B200_E_ARG;
+  if (d->algo < FRISK_B200_ALGO_AUTO || d->algo > FRISK_B200_ALGO_F32_SPLIT) return FRISK_B200_E_ARG;
   return 0;
 }
 
@@ -361,11 +361,12 @@ int frisk_b200_gemm_select(const frisk_b200_gemm_desc* d) {
   if (rc) return rc;
   if (d->algo != FRISK_B200_ALGO_AUTO) {
     if (d->algo == FRISK_B200_ALGO_SIMT_F32) return d->dtype_ab == FRISK_B200_F32 ? d->algo : FRISK_B200_E_UNSUPPORTED;
+    if (d->algo == FRISK_B200_ALGO_F32_SPLIT) return f32_split_supported(*d) ? d->algo : FRISK_B200_E_UNSUPPORTED;
     if (d->algo == FRISK_B200_ALGO_SKINNY) return skinny_supported(*d) ? d->algo : FRISK_B200_E_UNSUPPORTED;
     if (d->algo == FRISK_B200_ALGO_TCGEN05 || d->algo == FRISK_B200_ALGO_TCGEN05_PAIR)
       return tcgen05_supported(*d) ? d->algo : FRISK_B200_E_UNSUPPORTED;
   }
-  if (d->dtype_ab == FRISK_B200_F32) return FRISK_B200_ALGO_SIMT_F32;
+  if (d->dtype_ab == FRISK_B200_F32) return f32_split_preferred(*d) ? FRISK_B200_ALGO_F32_SPLIT : FRISK_B200_ALGO_SIMT_F32;
   if (skinny_supported(*d)) return FRISK_B200_ALGO_SKINNY;
   if (tcgen05_supported(*d)) return tcgen05_2cta_preferred(*d) ? FRISK_B200_ALGO_TCGEN05_PAIR : FRISK_B200_ALGO_TCGEN05;
   return FRISK_B200_E_ALIGN;  // 16-bit operands whose pitch is not a multiple of 16 bytes
@@ -391,11 +392,14 @@ int frisk_b200_gemm(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc* d, const vo
     case FRISK_B200_ALGO_SIMT_F32:
       return launch_gemm_simt_f32(ctx, *d, static_cast<const float*>(A), static_cast<const float*>(B),
                                   static_cast<float*>(C), s);
+    case FRISK_B200_ALGO_F32_SPLIT:
+      return launch_gemm_f32_split(ctx, *d, static_cast<const float*>(A), static_cast<const float*>(B),
+                                   static_cast<float*>(C), s);
     case FRISK_B200_ALGO_SKINNY: {
       size_t need = skinny_workspace_bytes(*d);
       if (!workspace) {
         // library-owned scratch: zeroed when (re)allocated, left clean by every launch
-        std::lock_guard<std::mutex> lock(ctx->mu);
+        std::lock_guard<std::recursive_mutex> lock(ctx->mu);
         (void)need;
         int rc = prepare_owned_skinny_ws(ctx, *d, s);
         if (rc) return rc;
@@ -410,7 +414,7 @@ int frisk_b200_gemm(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc* d, const vo
       size_t need = tcgen05_2cta_workspace_bytes(*d);
       if (need && !workspace) {
         // library-owned scratch: zeroed when allocated, tickets are left at zero by every launch
-        std::lock_guard<std::mutex> lock(ctx->mu);
+        std::lock_guard<std::recursive_mutex> lock(ctx->mu);
         int rc = ensure_stage(ctx, 5, need, true, s);
         if (rc) return rc;
         workspace = ctx->stage[5].ptr;
@@ -429,7 +433,7 @@ int frisk_b200_gemm_host(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc* d, con
   if (algo < 0) return algo;
   FB_DEVICE(ctx);
   GemmExtents e = gemm_extents(*d);
-  std::lock_guard<std::mutex> lock(ctx->mu);
+  std::lock_guard<std::recursive_mutex> lock(ctx->mu);
   int rc;
   if ((rc = ensure_stage(ctx, 0, e.a, false))) return rc;
   if ((rc = ensure_stage(ctx, 1, e.b, false))) return rc;
@@ -487,6 +491,10 @@ int frisk_b200_gemm_host(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc* d, con
       case FRISK_B200_ALGO_SIMT_F32:
         rc = launch_gemm_simt_f32(ctx, dp, reinterpret_cast<const float*>(dA), static_cast<const float*>(ctx->stage[1].ptr),
                                   reinterpret_cast<float*>(dC), s);
+        break;
+      case FRISK_B200_ALGO_F32_SPLIT:
+        rc = launch_gemm_f32_split(ctx, dp, reinterpret_cast<const float*>(dA), static_cast<const float*>(ctx->stage[1].ptr),
+                                   reinterpret_cast<float*>(dC), s);
         break;
       case FRISK_B200_ALGO_SKINNY:
         rc = launch_gemm_skinny(ctx, dp, dA, ctx->stage[1].ptr, dC, ctx->stage[3].ptr, ctx->stage[3].bytes, s);
@@ -560,7 +568,7 @@ int frisk_b200_attention_fwd_host(frisk_b200_ctx* ctx, const frisk_b200_attn_des
   size_t es = dtype_size(d->dtype_in), os = dtype_size(d->dtype_out);
   size_t qb = (size_t)d->B * d->H * d->S_q * d->D * es, kb = (size_t)d->B * d->H * d->S_kv * d->D * es;
   size_t ob = (size_t)d->B * d->H * d->S_q * d->D * os;
-  std::lock_guard<std::mutex> lock(ctx->mu);
+  std::lock_guard<std::recursive_mutex> lock(ctx->mu);
   if ((rc = ensure_stage(ctx, 0, qb, false))) return rc;
   if ((rc = ensure_stage(ctx, 1, kb, false))) return rc;
   if ((rc = ensure_stage(ctx, 2, ob, false))) return rc;
@@ -677,7 +685,7 @@ int frisk_b200_gemm_fused(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc* d, co
     ws_tail_bytes = tail;
     ws_part = reinterpret_cast<float*>(static_cast<unsigned char*>(workspace) + tail);
   } else {
-    std::lock_guard<std::mutex> lock(ctx->mu);
+    std::lock_guard<std::recursive_mutex> lock(ctx->mu);
     int rc;
     if (tail) {
       if ((rc = ensure_stage(ctx, 5, tail, true, s))) return rc;

@@ -73,12 +73,13 @@ struct frisk_b200_ctx {
   unsigned* d_status = nullptr;  // device status word (first failing wait records its code)
   unsigned* h_status = nullptr;  // pinned mirror
   // staging for the *_host entry points and library-owned workspace
-  fb::StagingBuffer stage[8];  // 0-2 A/B/C staging, 3 skinny scratch, 4 V staging, 5 GEMM tail scratch, 6 row partials, 7 fp32 stream-K scratch
+  fb::StagingBuffer stage[11];  // 0-2 A/B/C staging, 3 skinny scratch, 4 V staging, 5 GEMM tail scratch, 6 row partials,
+                                // 7 fp32 stream-K scratch, 8-10 fp32-on-tensor-cores: stacked A, stacked B, 3M x 3N product
   cudaStream_t host_stream = nullptr;
   cudaStream_t copy_stream = nullptr;
   cudaStream_t out_stream = nullptr;
   cudaEvent_t ev[24] = {};
-  std::mutex mu;
+  std::recursive_mutex mu;  // recursive: the *_host entries hold it while a launcher takes it for its scratch
   std::mutex tmap_mu;
   std::vector<fb::TmapEntry> tmaps;  // encoded TMA descriptors, most recently used (see TmapKey)
   uint64_t tmap_clock = 0;
@@ -165,6 +166,11 @@ inline GemmExtents gemm_extents(const frisk_b200_gemm_desc& d) {
 // ---- kernel launchers (one per .cu file) --------------------------------------------
 int launch_gemm_simt_f32(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc& d, const float* A, const float* B,
                          float* C, cudaStream_t s);
+// fp32 GEMM as nine bf16 tensor-core products of exactly split operands (gemm_f32_split.cu)
+bool f32_split_supported(const frisk_b200_gemm_desc& d);
+bool f32_split_preferred(const frisk_b200_gemm_desc& d);
+int launch_gemm_f32_split(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc& d, const float* A, const float* B,
+                          float* C, cudaStream_t s);
 
 // Decode-shape GEMM (gemm_skinny.cu).  Its scratch begins with one ticket per 128-column tile; the
 // kernel leaves them at zero, so they need clearing only when the scratch was last used with

@@ -468,7 +468,7 @@ int launch_gemm_simt_f32(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc& d, con
     // scratch: tickets (zero between launches: the finisher of a tile clears its ticket), then two slots per SM
     const size_t ticket_bytes = (size_t)kMaxStreamTiles * sizeof(unsigned);
     const size_t need = ticket_bytes + (size_t)ctx->num_sms * 2 * kTileFloats * sizeof(float);
-    std::lock_guard<std::mutex> lock(ctx->mu);
+    std::lock_guard<std::recursive_mutex> lock(ctx->mu);
     StagingBuffer& b = ctx->stage[7];
     if (!b.ptr) {
       FB_CUDA(ctx, cudaMalloc(&b.ptr, need));

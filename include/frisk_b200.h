@@ -45,7 +45,8 @@ enum {
   FRISK_B200_ALGO_SIMT_F32 = 1, /* fp32 CUDA-core GEMM                                   */
   FRISK_B200_ALGO_TCGEN05 = 2,  /* fp16/bf16 tcgen05 + TMEM + TMA ring, one CTA per tile */
   FRISK_B200_ALGO_SKINNY = 3,   /* M<=16: weights streamed by TMA into tcgen05, stream-K  */
-  FRISK_B200_ALGO_TCGEN05_PAIR = 4 /* tcgen05 with CTA pairs (cta_group::2), 256x256 tiles */
+  FRISK_B200_ALGO_TCGEN05_PAIR = 4, /* tcgen05 with CTA pairs (cta_group::2), 256x256 tiles */
+  FRISK_B200_ALGO_F32_SPLIT = 5 /* fp32 operands split exactly into 3 bf16 terms, 9 tcgen05 products, fp32 sums */
 };
 
 /* error codes (negative: host-side contract checks) */

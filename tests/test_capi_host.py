@@ -63,7 +63,15 @@ def test_rank_and_sign_checks():
 def test_kernel_selection_and_workspace():
     lib = capi.load()
     sel = lambda d: lib.frisk_b200_gemm_select(d)  # noqa: E731
-    assert sel(capi.gemm_desc(1024, 1024, 1024, "fp32")) == capi.ALGO_SIMT_F32
+    # fp32: the split-bf16 tensor-core path where it pays and the extents allow it, else the CUDA cores
+    assert sel(capi.gemm_desc(1024, 1024, 1024, "fp32")) == capi.ALGO_F32_SPLIT
+    assert sel(capi.gemm_desc(1024, 1024, 1024, "fp32", algo=capi.ALGO_SIMT_F32)) == capi.ALGO_SIMT_F32
+    assert sel(capi.gemm_desc(1024, 1024, 1023, "fp32")) == capi.ALGO_SIMT_F32      # extents not multiples of 8
+    assert sel(capi.gemm_desc(128, 1024, 1024, "fp32")) == capi.ALGO_SIMT_F32       # too small to pay for the passes
+    assert sel(capi.gemm_desc(128, 1024, 1024, "fp32", algo=capi.ALGO_F32_SPLIT)) == capi.ALGO_F32_SPLIT
+    assert sel(capi.gemm_desc(100, 77, 51, "fp32", algo=capi.ALGO_F32_SPLIT)) == -6
+    assert sel(capi.gemm_desc(64, 64, 64, "fp16", algo=capi.ALGO_F32_SPLIT)) == -6
+    assert sel(capi.gemm_desc(64, 64, 64, "fp32", algo=6)) == -7
     assert sel(capi.gemm_desc(4096, 4096, 4096, "fp16", trans_b=True)) == capi.ALGO_TCGEN05_PAIR
     assert sel(capi.gemm_desc(4096, 4096, 4096, "fp16")) == capi.ALGO_TCGEN05_PAIR
     assert sel(capi.gemm_desc(1024, 1024, 4096, "fp16", trans_b=True)) == capi.ALGO_TCGEN05  # too few 256x256 tiles for pairs

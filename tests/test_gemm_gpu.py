@@ -57,11 +57,46 @@ def check(ctx, M, N, K, dtype_ab, dtype_c, ta, tb, seed, accumulate=False, algo=
     return err
 
 
-# ------------------------------------------------------------------ fp32 SIMT
-def test_f32_config_1024(ctx):
+# ------------------------------------------------------------------ fp32: CUDA cores and split-bf16 tensor cores
+F32_ALGOS = [capi.ALGO_AUTO, capi.ALGO_SIMT_F32, capi.ALGO_F32_SPLIT]
+
+
+@pytest.mark.parametrize("algo", F32_ALGOS)
+def test_f32_config_1024(ctx, algo):
     spec = inputs.WORKLOADS["gemm_f32_1024"]
-    err = check(ctx, spec["M"], spec["N"], spec["K"], "fp32", "fp32", False, False, spec["seed"])
+    err = check(ctx, spec["M"], spec["N"], spec["K"], "fp32", "fp32", False, False, spec["seed"], algo=algo)
     assert err < 1e-5  # fp32 accumulation of 1024 terms is far inside the 1e-3 budget
+    # the tensor-core path adds nine exact-product GEMMs of a three-term bf16 split: fp32-GEMM accuracy
+    assert err < 2e-6 or algo == capi.ALGO_SIMT_F32, err
+
+
+@pytest.mark.parametrize("ta,tb", [(False, False), (False, True), (True, False), (True, True)])
+def test_f32_split_transposes_accumulate_unaligned(ctx, ta, tb):
+    S = capi.ALGO_F32_SPLIT
+    assert check(ctx, 264, 136, 72, "fp32", "fp32", ta, tb, 14, algo=S) < 2e-6
+    assert check(ctx, 520, 328, 200, "fp32", "fp32", ta, tb, 15, accumulate=True, algo=S) < 2e-6
+    assert check(ctx, 72, 264, 136, "fp32", "fp32", ta, tb, 16, algo=S, offset=4) < 2e-6  # scalar loads and stores
+    with pytest.raises(ValueError):
+        check(ctx, 100, 77, 51, "fp32", "fp32", ta, tb, 11, algo=S)  # extents must be multiples of 8
+
+
+@pytest.mark.parametrize("ta,tb", [(False, False), (False, True), (True, False), (True, True)])
+def test_f32_simt_shared_k_ranges(ctx, ta, tb):
+    """Shapes whose tiles are fewer than the SMs or do not divide among them: every tile's k range is shared
+    between workers (tickets, partial tiles), with ragged edges and a ragged last k stage."""
+    S = capi.ALGO_SIMT_F32
+    check(ctx, 520, 328, 200, "fp32", "fp32", ta, tb, 15, accumulate=True, algo=S)
+    check(ctx, 130, 70, 1500, "fp32", "fp32", ta, tb, 17, algo=S)
+    check(ctx, 64, 64, 9000, "fp32", "fp32", ta, tb, 18, algo=S)          # one tile, 141 stages over 141 workers
+    check(ctx, 1024, 1024, 96, "fp32", "fp32", ta, tb, 19, algo=S)       # 256 tiles of two stages
+
+
+def test_f32_simt_rerun_is_bit_identical(ctx):
+    a, b = inputs.gemm_inputs(1024, 1024, 1024, "fp32", False, False, 5, "uniform")
+    first, ok1 = run_gemm(ctx, a, b, "fp32", "fp32", 1024, 1024, 1024, False, False, algo=capi.ALGO_SIMT_F32)
+    for _ in range(3):
+        again, ok2 = run_gemm(ctx, a, b, "fp32", "fp32", 1024, 1024, 1024, False, False, algo=capi.ALGO_SIMT_F32)
+        assert ok1 and ok2 and np.array_equal(first, again)
 
 
 def test_f32_config_1024_built_through_the_ir_builders(ctx):
