@@ -265,6 +265,6 @@ def export(module, contracts=True):
 
 def execute(packet, q, k, v, o, stream=None):
     """Run a packet on CUDA tensors bound to its four global roots (query, keys, values, output)."""
-    from . import execute as _execute
+    from .execute import execute as run_module   # the package attribute `execute` is that function, not the module
     module, _ = to_kernel(packet)
-    return _execute.execute(module, q, k, v, o, stream=stream)
+    return run_module(module, q, k, v, o, stream=stream)
