@@ -66,6 +66,17 @@ __device__ __forceinline__ uint32_t pack2<__nv_bfloat162, __nv_bfloat16>(float a
   __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
   return *reinterpret_cast<uint32_t*>(&h);
 }
+// two fp32 values rounded to TO and packed (16-bit TO only; the float form exists so that templates compile)
+template <typename TO>
+__device__ __forceinline__ uint32_t pack_out(float a, float b);
+template <>
+__device__ __forceinline__ uint32_t pack_out<__half>(float a, float b) { return pack2<__half2, __half>(a, b); }
+template <>
+__device__ __forceinline__ uint32_t pack_out<__nv_bfloat16>(float a, float b) {
+  return pack2<__nv_bfloat162, __nv_bfloat16>(a, b);
+}
+template <>
+__device__ __forceinline__ uint32_t pack_out<float>(float a, float) { return __float_as_uint(a); }
 __device__ __forceinline__ float2 unpack2(uint32_t u, __half) {
   return __half22float2(*reinterpret_cast<__half2*>(&u));
 }

@@ -18,6 +18,8 @@
 //   warp 0    TMA producer (both CTAs)         warp 1   MMA issuer (leader CTA only)
 //   warps 2-5 epilogue (both CTAs, own rows)
 
+#include <type_traits>
+
 #include "common.cuh"
 #include "gemm_common.cuh"
 #include "ptx.cuh"
@@ -48,7 +50,12 @@ struct Smem2 {
   static constexpr int kPushWarpBytes = 32 * kPushRowFloats * 4;
   static constexpr int kPushOffset = kBarOffset + 256;
   static constexpr int kTotalPush = kTotal + 4 * kPushWarpBytes;
+  // TMA-store mode only: two [32 rows][128 bytes] output boxes per epilogue warp, 1024-byte aligned
+  static constexpr int kOutOffset = kBarOffset + 1024;
+  static constexpr int kOutWarpBytes = 2 * 32 * 128;
+  static constexpr int kTotalOut = kOutOffset + 4 * kOutWarpBytes + 1024;
 };
+static_assert(Smem2::kTotalOut <= 232448, "the output boxes must fit next to the operand ring");
 
 // ---- cluster / cta_group::2 primitives
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -123,12 +130,12 @@ __device__ __forceinline__ Item2 get_item2(int i, int n_full, int num_kb) {
 
 // MODE: what the epilogue does with a finished tile.  Separate instantiations, so that the plain
 // store keeps its register budget and code exactly as if the other two did not exist.
-enum { kStore = 0, kPush = 1, kFused = 2 };
+enum { kStore = 0, kPush = 1, kFused = 2, kStoreTma = 3 };
 
 template <typename TO, bool BF16, bool A_MN, bool B_MN, int MODE>
 __global__ void __launch_bounds__(kThreads2, 1)
     gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                             TO* __restrict__ C, int M, int N, int K, int64_t ldc, int accumulate, int vec_c,
+                             const __grid_constant__ CUtensorMap tmap_c, TO* __restrict__ C, int M, int N, int K, int64_t ldc, int accumulate, int vec_c,
                              int n_full, int n_items, float* __restrict__ partials,
                              unsigned* __restrict__ tickets, const PushTargets push, const EpilogueArgs epi,
                              unsigned* __restrict__ status) {
@@ -165,6 +172,7 @@ __global__ void __launch_bounds__(kThreads2, 1)
     mbar_fence_init();
     tma_prefetch_desc(&tmap_a);
     tma_prefetch_desc(&tmap_b);
+    if (MODE == kStoreTma) tma_prefetch_desc(&tmap_c);
   }
   if (warp == 1) {
     tmem_alloc_pair(tmem_slot, 512);
@@ -322,7 +330,66 @@ __global__ void __launch_bounds__(kThreads2, 1)
       if (MODE == kFused)
         row_acc = epi.reduce_kind == FRISK_B200_REDUCE_MAX ? -INFINITY
                   : epi.reduce_kind == FRISK_B200_REDUCE_MIN ? INFINITY : 0.f;
-      if (write_c) {
+      if (MODE == kStoreTma && write_c) {
+        // Plain store through shared memory: a lane holds 128 bytes of ONE row, the warp writes them as a
+        // [32 rows][128 bytes] box in the 128-byte-swizzle image and one lane hands the box to the TMA unit,
+        // which writes whole lines and clips the box at the edges of C.  Two boxes per warp alternate.
+        constexpr int kUnitCols = 128 / (int)sizeof(TO);
+        unsigned char* boxes = smem + L::kOutOffset + quad * L::kOutWarpBytes;
+#pragma unroll 1
+        for (int u = 0; u < BN2 / kUnitCols; ++u) {
+          uint32_t w[32];
+          if (sizeof(TO) == 4) {
+            tmem_ld_32x32b_x32(taddr + u * 32, w);
+            tmem_ld_wait();
+            if (other != nullptr) {
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                const float4 o = __ldcg(other + (u * 8 + i) * BMC);
+                w[4 * i] = __float_as_uint(__uint_as_float(w[4 * i]) + o.x);
+                w[4 * i + 1] = __float_as_uint(__uint_as_float(w[4 * i + 1]) + o.y);
+                w[4 * i + 2] = __float_as_uint(__uint_as_float(w[4 * i + 2]) + o.z);
+                w[4 * i + 3] = __float_as_uint(__uint_as_float(w[4 * i + 3]) + o.w);
+              }
+            }
+          } else {
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+              uint32_t v[32];
+              tmem_ld_32x32b_x32(taddr + u * 64 + hh * 32, v);
+              tmem_ld_wait();
+              if (other != nullptr) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                  const float4 o = __ldcg(other + ((u * 2 + hh) * 8 + i) * BMC);
+                  v[4 * i] = __float_as_uint(__uint_as_float(v[4 * i]) + o.x);
+                  v[4 * i + 1] = __float_as_uint(__uint_as_float(v[4 * i + 1]) + o.y);
+                  v[4 * i + 2] = __float_as_uint(__uint_as_float(v[4 * i + 2]) + o.z);
+                  v[4 * i + 3] = __float_as_uint(__uint_as_float(v[4 * i + 3]) + o.w);
+                }
+              }
+#pragma unroll
+              for (int i = 0; i < 16; ++i)
+                w[hh * 16 + i] = pack_out<TO>(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
+            }
+          }
+          // the box written two units ago has been read by its store
+          if (lane == 0) tma_store_wait_read<1>();
+          __syncwarp();
+          unsigned char* box = boxes + (u & 1) * (32 * 128);
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            *reinterpret_cast<uint4*>(box + lane * 128 + ((j ^ (lane & 7)) << 4)) =
+                make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+          fence_proxy_async_smem();
+          __syncwarp();
+          const int c0 = n0 + u * kUnitCols, r0 = m0 + quad * 32;
+          if (lane == 0 && c0 < N && r0 < M) {
+            tma_store_2d(&tmap_c, box, c0, r0);
+            tma_store_commit();
+          }
+        }
+      } else if (write_c) {
 #pragma unroll 1
         for (int c = 0; c < BN2 / 32; ++c) {
           uint32_t v[32];
@@ -401,6 +468,7 @@ __global__ void __launch_bounds__(kThreads2, 1)
         acc_phase ^= 1;
       }
     }
+    if (MODE == kStoreTma && lane == 0) tma_store_wait<0>();  // the boxes are read and written out before the CTA leaves
   }
 
   // ------------------------------------------------------------------ teardown
@@ -464,8 +532,17 @@ int launch_cfg2(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc& d, const void* 
     rc = encode_tmap_2d(ctx, &tb, d.dtype_ab, B, (uint64_t)g.K, (uint64_t)g.N, (uint64_t)g.ldb * 2, BK, BNC, true);
   if (rc) { ctx->last_cuda = rc; return FRISK_B200_E_CUDA; }
 
+  CUtensorMap tc = ta;  // unused by the other modes
+  if (MODE == kStoreTma) {
+    // C as [M][N] with boxes of 32 rows x 128 bytes in the 128-byte-swizzle image the epilogue writes
+    const int out_dtype = sizeof(TO) == 4 ? FRISK_B200_F32 : (std::is_same<TO, __half>::value ? FRISK_B200_F16 : FRISK_B200_BF16);
+    rc = encode_tmap_2d(ctx, &tc, out_dtype, C, (uint64_t)g.N, (uint64_t)g.M, (uint64_t)g.ldc * sizeof(TO),
+                        128 / sizeof(TO), 32, true);
+    if (rc) { ctx->last_cuda = rc; return FRISK_B200_E_CUDA; }
+  }
+
   auto kern = gemm_tcgen05_2cta_kernel<TO, BF16, A_MN, B_MN, MODE>;
-  constexpr int kSmemBytes = MODE == kPush ? Smem2::kTotalPush : Smem2::kTotal;
+  constexpr int kSmemBytes = MODE == kPush ? Smem2::kTotalPush : MODE == kStoreTma ? Smem2::kTotalOut : Smem2::kTotal;
   cudaLaunchConfig_t cfg = {};
   cudaLaunchAttribute attr[2];
   attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -515,7 +592,7 @@ int launch_cfg2(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc& d, const void* 
   int64_t ldc = g.ldc;
   unsigned* st = ctx->d_status;
   int n_full = tp.n_full, n_items = tp.n_items;
-  FB_CUDA(ctx, cudaLaunchKernelEx(&cfg, kern, ta, tb, Cp, Mi, Ni, Ki, ldc, acc, vec_c, n_full, n_items, partials,
+  FB_CUDA(ctx, cudaLaunchKernelEx(&cfg, kern, ta, tb, tc, Cp, Mi, Ni, Ki, ldc, acc, vec_c, n_full, n_items, partials,
                                   tickets, push, epi, st));
   return 0;
 }
@@ -574,6 +651,18 @@ int launch_gemm_tcgen05_2cta(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc& d,
     if (bf) return launch_major2<__nv_bfloat16, true, kFused>(ctx, d, A, B, C, ws, ws_bytes, s, epi);
     return launch_major2<__half, false, kFused>(ctx, d, A, B, C, ws, ws_bytes, s, epi);
   }
+  // an overwriting store of a C whose base and row pitch are 16-byte aligned goes out through the TMA unit
+  const GemmDims g = resolve_dims(d);
+  const size_t cs = dtype_size(d.dtype_c);
+#ifndef FB_NO_TMA_STORE
+  if (d.clear_accum && aligned16(C) && (g.ldc * cs) % 16 == 0) {
+    if (d.dtype_c == FRISK_B200_F32)
+      return bf ? launch_major2<float, true, kStoreTma>(ctx, d, A, B, C, ws, ws_bytes, s, nullptr)
+                : launch_major2<float, false, kStoreTma>(ctx, d, A, B, C, ws, ws_bytes, s, nullptr);
+    if (bf) return launch_major2<__nv_bfloat16, true, kStoreTma>(ctx, d, A, B, C, ws, ws_bytes, s, nullptr);
+    return launch_major2<__half, false, kStoreTma>(ctx, d, A, B, C, ws, ws_bytes, s, nullptr);
+  }
+#endif
   if (d.dtype_c == FRISK_B200_F32)
     return bf ? launch_major2<float, true, kStore>(ctx, d, A, B, C, ws, ws_bytes, s, nullptr)
               : launch_major2<float, false, kStore>(ctx, d, A, B, C, ws, ws_bytes, s, nullptr);
