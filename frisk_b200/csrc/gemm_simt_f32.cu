@@ -1,14 +1,15 @@
 // fp32 GEMM on the CUDA cores: C <- (clear_accum ? 0 : C) + op(A).op(B), fp32 throughout.
 // Contract: `frisk.gemm` with f32 operands (lib/Dialect/Frisk/IR/FriskOps.cpp:406-426).
 //
-// One CTA of 64*KG threads per SM computes 64x64 output tiles.  The CTA is KG "k-groups" of two
-// warps; a pipeline stage holds 8*KG k of the A and B tiles in shared memory ([k][m] and [k][n],
-// whichever way the operand lies in global memory) and k-group g multiplies rows [8g, 8g+8) of
-// it, every thread owning an 8x8 register tile (two 4-row groups x two 4-column groups, so that a
-// half-warp's 128-bit fragment read touches at most 128 contiguous bytes).  The KG partial
-// tiles are added through shared memory when a tile's k range ends.  Small CTA tiles keep the
-// tile count above the SM count for the small problems this path serves, the 8x8 register
-// tile keeps two shared-memory wavefronts per 16 FMA instructions.
+// One CTA of 256 threads per SM computes 64x64 output tiles.  The CTA is four "k-groups" of two
+// warps; a pipeline stage holds 64 k of the A and B tiles in shared memory ([k][m] and [k][n],
+// whichever way the operand lies in global memory) and k-group g multiplies rows [16g, 16g+16) of
+// it, every thread owning an 8x8 register tile (two 4-row groups x two 4-column groups: the 32
+// lanes of a 128-bit fragment read touch at most 128 distinct bytes, which the shared memory
+// delivers in one cycle).  The four partial tiles are added through shared memory when a tile's
+// k range ends.  Small CTA tiles keep the tile count above the SM count for the small problems
+// this path serves; one CTA per SM leaves each thread up to 255 registers, so the next stage's
+// operand fetches and the next k-step's fragments stay in flight across the multiply.
 //
 // Work is split stream-K style: unit = (tile, k-stage); the units are numbered tile-major and
 // worker c takes the contiguous range [start(c), start(c+1)), so every SM multiplies the same

@@ -31,10 +31,6 @@ constexpr int BK = 64;       // one 128-byte swizzle span of 16-bit elements
 constexpr int UMMA_K = 16;
 constexpr int kStages = 4;
 constexpr int kThreads = 192;
-// k-blocks between an optional L2 prefetch and the shared-memory load.  Measured on B200 at
-// 4096^3: 0 (off) 1250 TFLOP/s, 2: 946, 4: 952, 16: 1016 -- the prefetches compete with the
-// loads for the TMA unit, so it stays off; FRISK_B200_GEMM_PREFETCH overrides for experiments.
-constexpr int kPrefetchAhead = 0;
 
 template <int BN>
 struct SmemLayout {
@@ -72,7 +68,7 @@ template <typename TO, int BN, bool BF16, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(kThreads, 1)
     gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                         TO* __restrict__ C, int M, int N, int K, int64_t ldc, int accumulate, int vec_c,
-                        int n_full, int n_items, int prefetch_ahead, unsigned* __restrict__ status) {
+                        int n_full, int n_items, unsigned* __restrict__ status) {
   using L = SmemLayout<BN>;
   extern __shared__ unsigned char smem_unaligned[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(
@@ -121,22 +117,6 @@ __global__ void __launch_bounds__(kThreads, 1)
         const Item it = get_item<BN>(t, n_full, tiles_m, tiles_n);
         const int m0 = it.m0, n0 = it.n0;
         for (int kb = 0; kb < num_kb; ++kb) {
-          // pull a k-block that is several ring depths ahead into L2, so that the ring itself
-          // only has to cover L2 latency
-          if (prefetch_ahead > 0 && kb + prefetch_ahead < num_kb) {
-            const int kp = (kb + prefetch_ahead) * BK;
-            if (A_MN) {
-#pragma unroll
-              for (int j = 0; j < BM / 64; ++j) tma_prefetch_l2_2d(&tmap_a, m0 + j * 64, kp);
-            } else {
-              tma_prefetch_l2_2d(&tmap_a, kp, m0);
-            }
-            if (B_MN) {
-              for (int j = 0; j < it.bn / 64; ++j) tma_prefetch_l2_2d(&tmap_b, n0 + j * 64, kp);
-            } else {
-              for (int j = 0; j < it.bn / 128; ++j) tma_prefetch_l2_2d(&tmap_b, kp, n0 + j * 128);
-            }
-          }
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, status, ST_TIMEOUT_EMPTY)) {
             ok = false;
             break;
@@ -294,10 +274,9 @@ int launch_cfg(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc& d, const void* A
     n_full = tiles - rem;
     n_items = n_full + 2 * rem;
   }
-  int prefetch = kPrefetchAhead;
   int vec_c = aligned16(C) && (g.ldc * sizeof(TO)) % 16 == 0;
   kern<<<grid, kThreads, L::kTotal, s>>>(ta, tb, static_cast<TO*>(C), (int)g.M, (int)g.N, (int)g.K, g.ldc,
-                                         d.clear_accum ? 0 : 1, vec_c, n_full, n_items, prefetch, ctx->d_status);
+                                         d.clear_accum ? 0 : 1, vec_c, n_full, n_items, ctx->d_status);
   FB_CUDA(ctx, cudaGetLastError());
   return 0;
 }
