@@ -39,7 +39,9 @@ typedef struct frisk_b200_ctx frisk_b200_ctx;
 /* element types: the float types python/frisk/common/utils.py:156-170 can name */
 enum { FRISK_B200_F32 = 0, FRISK_B200_F16 = 1, FRISK_B200_BF16 = 2 };
 
-/* kernel selection for frisk_b200_gemm (AUTO picks by type and shape) */
+/* kernel selection for frisk_b200_gemm (AUTO picks by type and shape).  f32 operands: AUTO takes F32_SPLIT when
+ * M, N and K are multiples of 8 and at least 256, else SIMT_F32.  F32_SPLIT and SIMT_F32 keep their scratch (stacked
+ * bf16 operands and the 3M x 3N fp32 product; tickets and partial tiles) in the context, whatever `workspace` is. */
 enum {
   FRISK_B200_ALGO_AUTO = 0,
   FRISK_B200_ALGO_SIMT_F32 = 1, /* fp32 CUDA-core GEMM                                   */
