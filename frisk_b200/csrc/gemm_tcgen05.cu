@@ -17,6 +17,8 @@
 // inference proposes for 16-bit MMA operands
 // (lib/Dialect/Frisk/Target/SM90/SM90GemmConstraints.cpp:121-138); TMA writes them directly.
 // No TMA load uses cluster multicast.
+#include <type_traits>
+
 #include "common.cuh"
 
 #include "gemm_common.cuh"
@@ -39,6 +41,11 @@ struct SmemLayout {
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kBarOffset = kStages * kStageBytes;
   static constexpr int kTotal = kBarOffset + 256 + 1024;  // barriers + alignment slack
+  // TMA-store epilogue only: two [32 rows][128 bytes] output boxes per epilogue warp, 1024-byte aligned
+  static constexpr int kOutOffset = kBarOffset + 1024;
+  static constexpr int kOutWarpBytes = 2 * 32 * 128;
+  static constexpr int kTotalOut = kOutOffset + 4 * kOutWarpBytes + 1024;
+  static_assert(kTotalOut <= 232448, "the output boxes must fit next to the operand ring");
 };
 
 // Work items: the first n_full items are whole 128xBN tiles; the tiles that would form a
@@ -64,10 +71,11 @@ __device__ __forceinline__ Item get_item(int idx, int n_full, int tiles_m, int t
 }
 
 // A_MN / B_MN: the operand is contiguous along M / N in global memory (MN-major image).
-template <typename TO, int BN, bool BF16, bool A_MN, bool B_MN>
+// TMA_OUT: an overwriting store of an aligned C leaves through shared-memory boxes and TMA stores.
+template <typename TO, int BN, bool BF16, bool A_MN, bool B_MN, bool TMA_OUT>
 __global__ void __launch_bounds__(kThreads, 1)
     gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                        TO* __restrict__ C, int M, int N, int K, int64_t ldc, int accumulate, int vec_c,
+                        const __grid_constant__ CUtensorMap tmap_c, TO* __restrict__ C, int M, int N, int K, int64_t ldc, int accumulate, int vec_c,
                         int n_full, int n_items, unsigned* __restrict__ status) {
   using L = SmemLayout<BN>;
   extern __shared__ unsigned char smem_unaligned[];
@@ -97,6 +105,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     mbar_fence_init();
     tma_prefetch_desc(&tmap_a);
     tma_prefetch_desc(&tmap_b);
+    if (TMA_OUT) tma_prefetch_desc(&tmap_c);
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, 2 * BN);
@@ -106,6 +115,10 @@ __global__ void __launch_bounds__(kThreads, 1)
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  // Launched with programmatic stream serialization: the set-up above may run while the kernel in front of
+  // this one drains; nothing touches global memory before that kernel is complete.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -195,6 +208,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   } else {
     // ------------------------------------------------------------------ epilogue
     const int quad = warp & 3;  // TMEM lanes [32*quad, 32*quad+32) are this warp's
+    int box_sel = 0;            // which of the warp's two output boxes the next TMA store uses
     int acc = 0;
     uint32_t acc_phase = 0;
     for (int t = blockIdx.x; t < n_items; t += gridDim.x) {
@@ -204,14 +218,55 @@ __global__ void __launch_bounds__(kThreads, 1)
       tc_fence_after_sync();
       const int row = m0 + quad * 32 + lane;
       const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(quad * 32) << 16);
+      if (TMA_OUT) {
+        // a lane holds 128 bytes of ONE row; the warp writes its 32 rows as a 128-byte-swizzle box and one lane
+        // hands the box to the TMA unit, which writes whole lines and clips at the edges of C
+        constexpr int kUnitCols = 128 / (int)sizeof(TO);
+        unsigned char* boxes = smem + L::kOutOffset + quad * L::kOutWarpBytes;
 #pragma unroll 1
-      for (int c = 0; c < it.bn / 32; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32b_x32(taddr + c * 32, v);
-        tmem_ld_wait();
-        const int col = n0 + c * 32;
-        if (row < M && col < N)
-          store_row_chunk<TO>(C + (int64_t)row * ldc + col, v, min(32, N - col), vec_c != 0, accumulate != 0);
+        for (int u = 0; u < it.bn / kUnitCols; ++u) {
+          const int c0 = n0 + u * kUnitCols, r0 = m0 + quad * 32;
+          if (c0 >= N || r0 >= M) break;  // wholly outside C (warp-uniform)
+          uint32_t w[32];
+          if (sizeof(TO) == 4) {
+            tmem_ld_32x32b_x32(taddr + u * 32, w);
+            tmem_ld_wait();
+          } else {
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+              uint32_t v[32];
+              tmem_ld_32x32b_x32(taddr + u * 64 + hh * 32, v);
+              tmem_ld_wait();
+#pragma unroll
+              for (int i = 0; i < 16; ++i)
+                w[hh * 16 + i] = pack_out<TO>(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
+            }
+          }
+          if (lane == 0) tma_store_wait_read<1>();  // the store before the last one used this box: it has been read
+          __syncwarp();
+          unsigned char* box = boxes + box_sel * (32 * 128);
+          box_sel ^= 1;
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            *reinterpret_cast<uint4*>(box + lane * 128 + ((j ^ (lane & 7)) << 4)) =
+                make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_2d(&tmap_c, box, c0, r0);
+            tma_store_commit();
+          }
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < it.bn / 32; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32b_x32(taddr + c * 32, v);
+          tmem_ld_wait();
+          const int col = n0 + c * 32;
+          if (row < M && col < N)
+            store_row_chunk<TO>(C + (int64_t)row * ldc + col, v, min(32, N - col), vec_c != 0, accumulate != 0);
+        }
       }
       tc_fence_before_sync();
       __syncwarp();
@@ -221,6 +276,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         acc_phase ^= 1;
       }
     }
+    if (TMA_OUT && lane == 0) tma_store_wait<0>();  // the boxes are read and written out before the CTA leaves
   }
 
   // ------------------------------------------------------------------ teardown
@@ -257,13 +313,16 @@ int launch_cfg(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc& d, const void* A
     rc = encode_tmap_2d(ctx, &tb, d.dtype_ab, B, (uint64_t)g.K, (uint64_t)g.N, (uint64_t)g.ldb * 2, BK, 128, true);
   if (rc) { if (ctx) ctx->last_cuda = rc; return FRISK_B200_E_CUDA; }
 
-  auto kern = gemm_tcgen05_kernel<TO, BN, BF16, A_MN, B_MN>;
+  // an overwriting store of a C whose base and row pitch are 16-byte aligned goes out through the TMA unit
+  const bool tma_out = d.clear_accum && aligned16(C) && (g.ldc * sizeof(TO)) % 16 == 0;
+  CUtensorMap tc = ta;  // unused otherwise
+  if (tma_out) {
+    const int out_dtype = sizeof(TO) == 4 ? FRISK_B200_F32 : (std::is_same<TO, __half>::value ? FRISK_B200_F16 : FRISK_B200_BF16);
+    rc = encode_tmap_2d(ctx, &tc, out_dtype, C, (uint64_t)g.N, (uint64_t)g.M, (uint64_t)g.ldc * sizeof(TO),
+                        128 / sizeof(TO), 32, true);
+    if (rc) { if (ctx) ctx->last_cuda = rc; return FRISK_B200_E_CUDA; }
+  }
   using L = SmemLayout<BN>;
-  static PerDeviceOnce opt_in;  // one per instantiation
-  if (opt_in(ctx->device, [&] {
-        return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal) == cudaSuccess ? 0 : 1;
-      }))
-    return FRISK_B200_E_CUDA;
   int tiles = (int)(((g.M + BM - 1) / BM) * ((g.N + BN - 1) / BN));
   int grid = tiles < ctx->num_sms ? tiles : ctx->num_sms;
   // A partial last wave of at most grid/2 tiles runs as twice as many half-width items: the
@@ -275,10 +334,31 @@ int launch_cfg(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc& d, const void* A
     n_items = n_full + 2 * rem;
   }
   int vec_c = aligned16(C) && (g.ldc * sizeof(TO)) % 16 == 0;
-  kern<<<grid, kThreads, L::kTotal, s>>>(ta, tb, static_cast<TO*>(C), (int)g.M, (int)g.N, (int)g.K, g.ldc,
-                                         d.clear_accum ? 0 : 1, vec_c, n_full, n_items, ctx->d_status);
-  FB_CUDA(ctx, cudaGetLastError());
-  return 0;
+  auto launch = [&](auto kern, int smem_bytes, PerDeviceOnce& opt_in) -> int {
+    if (opt_in(ctx->device, [&] {
+          return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes) == cudaSuccess ? 0 : 1;
+        }))
+      return FRISK_B200_E_CUDA;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = smem_bytes;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;  // the kernel waits (griddepcontrol.wait) itself
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    TO* Cp = static_cast<TO*>(C);
+    int Mi = (int)g.M, Ni = (int)g.N, Ki = (int)g.K, acc = d.clear_accum ? 0 : 1;
+    int64_t ldc = g.ldc;
+    unsigned* st = ctx->d_status;
+    FB_CUDA(ctx, cudaLaunchKernelEx(&cfg, kern, ta, tb, tc, Cp, Mi, Ni, Ki, ldc, acc, vec_c, n_full, n_items, st));
+    return 0;
+  };
+  static PerDeviceOnce opt_in_plain, opt_in_tma;  // one pair per instantiation
+  if (tma_out) return launch(gemm_tcgen05_kernel<TO, BN, BF16, A_MN, B_MN, true>, L::kTotalOut, opt_in_tma);
+  return launch(gemm_tcgen05_kernel<TO, BN, BF16, A_MN, B_MN, false>, L::kTotal, opt_in_plain);
 }
 
 template <typename TO, int BN, bool BF16>

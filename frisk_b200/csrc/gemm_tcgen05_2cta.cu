@@ -278,6 +278,7 @@ __global__ void __launch_bounds__(kThreads2, 1)
   } else {
     // ------------------------------------------------------------------ epilogue (own 128 rows)
     const int quad = warp & 3;
+    int box_sel = 0;  // which of the warp's two output boxes the next TMA store uses
     int acc = 0;
     uint32_t acc_phase = 0;
     const uint32_t leader_acc_empty0 = mapa_u32(&acc_empty[0], 0), leader_acc_empty1 = mapa_u32(&acc_empty[1], 0);
@@ -338,6 +339,8 @@ __global__ void __launch_bounds__(kThreads2, 1)
         unsigned char* boxes = smem + L::kOutOffset + quad * L::kOutWarpBytes;
 #pragma unroll 1
         for (int u = 0; u < BN2 / kUnitCols; ++u) {
+          const int c0 = n0 + u * kUnitCols, r0 = m0 + quad * 32;
+          if (c0 >= N || r0 >= M) break;  // wholly outside C (warp-uniform)
           uint32_t w[32];
           if (sizeof(TO) == 4) {
             tmem_ld_32x32b_x32(taddr + u * 32, w);
@@ -373,18 +376,18 @@ __global__ void __launch_bounds__(kThreads2, 1)
                 w[hh * 16 + i] = pack_out<TO>(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
             }
           }
-          // the box written two units ago has been read by its store
+          // the store before the last one used this box: it has been read
           if (lane == 0) tma_store_wait_read<1>();
           __syncwarp();
-          unsigned char* box = boxes + (u & 1) * (32 * 128);
+          unsigned char* box = boxes + box_sel * (32 * 128);
+          box_sel ^= 1;
 #pragma unroll
           for (int j = 0; j < 8; ++j)
             *reinterpret_cast<uint4*>(box + lane * 128 + ((j ^ (lane & 7)) << 4)) =
                 make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
           fence_proxy_async_smem();
           __syncwarp();
-          const int c0 = n0 + u * kUnitCols, r0 = m0 + quad * 32;
-          if (lane == 0 && c0 < N && r0 < M) {
+          if (lane == 0) {
             tma_store_2d(&tmap_c, box, c0, r0);
             tma_store_commit();
           }

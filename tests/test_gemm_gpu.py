@@ -181,6 +181,17 @@ def test_tc_tail_wave_of_half_tiles(ctx, tb):
     check(ctx, 2048, 2400, 64, "fp16", "fp32", False, tb, 30, algo=capi.ALGO_TCGEN05, dist="normal_rsqrt_k")
 
 
+@pytest.mark.parametrize("algo", [capi.ALGO_TCGEN05, capi.ALGO_TCGEN05_PAIR])
+@pytest.mark.parametrize("dtype_c", ["fp16", "fp32"])
+def test_tc_store_boxes_at_ragged_edges(ctx, algo, dtype_c):
+    """Overwriting stores leave as 32-row x 128-byte boxes through TMA: tiles whose last boxes lie partly or wholly
+    outside C (ragged M and N), several tiles per CTA so that the two boxes of a warp are reused across tiles."""
+    check(ctx, 2100, 2400, 64, "fp16", dtype_c, False, True, 41, algo=algo, dist="normal_rsqrt_k")
+    check(ctx, 5000, 4904, 128, "bf16", "bf16" if dtype_c == "fp16" else "fp32", False, True, 42, algo=algo,
+          dist="normal_rsqrt_k")
+    check(ctx, 300, 520, 96, "fp16", dtype_c, False, False, 43, algo=algo, dist="normal_rsqrt_k")
+
+
 @pytest.mark.parametrize("tb", [True, False])
 def test_tc_pair_tail_wave_split_in_k(ctx, tb):
     # 8 x 10 = 80 tiles of 256x256 on 74 CTA pairs: the 6 tiles of the last wave run as 12 K halves
