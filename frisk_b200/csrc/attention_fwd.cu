@@ -48,14 +48,18 @@ struct AttnSmem {
   static constexpr int kK = 2 * kTileBytes;            // K stages
   static constexpr int kV = kK + kStagesKV * kTileBytes;
   static constexpr int kBar = kV + kStagesKV * kTileBytes;
-  static constexpr int kTotal = kBar + 256 + 1024;
+  // 16-bit outputs: one [32 rows][128 bytes] box per softmax warp for the TMA stores of O, 1024-byte aligned
+  static constexpr int kOut = kBar + 1024;
+  static constexpr int kTotal = kOut + 8 * (32 * 128) + 1024;
+  static_assert(kTotal <= 232448, "the output boxes must fit next to the Q, K and V tiles");
 };
 
 
 template <bool BF16, int D, bool OUT_F32, bool NORM>
 __global__ void __launch_bounds__(kThreads, 1)
     attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
-                         const __grid_constant__ CUtensorMap tmap_v, const AttnParams p) {
+                         const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_o,
+                         const AttnParams p) {
   using L = AttnSmem<D>;
   constexpr int kBoxes = D / 64;            // 64-element (128-byte) column blocks per tile
   constexpr int kBoxBytes = BM * 128;       // one [128 rows][128 B] block
@@ -535,6 +539,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         const float inv = 1.0f / l_sum;
         const bool valid = g_row < p.S_q;
         const size_t row_off = ((size_t)bh * p.S_q + (size_t)min(g_row, p.S_q - 1)) * D;
+        uint32_t packed[32];
 #pragma unroll
         for (int c = 0; c < D / 32; ++c) {
           uint32_t o[32];
@@ -547,16 +552,29 @@ __global__ void __launch_bounds__(kThreads, 1)
               for (int i = 0; i < 8; ++i)
                 dst[i] = make_float4(__uint_as_float(o[4 * i]) * inv, __uint_as_float(o[4 * i + 1]) * inv,
                                      __uint_as_float(o[4 * i + 2]) * inv, __uint_as_float(o[4 * i + 3]) * inv);
-            } else {
-              uint4* dst = reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.O) + row_off + c * 32);
+            }
+          }
+          if (!OUT_F32) {
+            // the 32 scaled values of this lane's row, rounded: half of a 128-byte box row
 #pragma unroll
-              for (int i = 0; i < 4; ++i) {
-                uint4 v;
-                v.x = pack16<BF16>(__uint_as_float(o[8 * i]) * inv, __uint_as_float(o[8 * i + 1]) * inv);
-                v.y = pack16<BF16>(__uint_as_float(o[8 * i + 2]) * inv, __uint_as_float(o[8 * i + 3]) * inv);
-                v.z = pack16<BF16>(__uint_as_float(o[8 * i + 4]) * inv, __uint_as_float(o[8 * i + 5]) * inv);
-                v.w = pack16<BF16>(__uint_as_float(o[8 * i + 6]) * inv, __uint_as_float(o[8 * i + 7]) * inv);
-                dst[i] = v;
+            for (int i = 0; i < 16; ++i)
+              packed[(c & 1) * 16 + i] = pack16<BF16>(__uint_as_float(o[2 * i]) * inv, __uint_as_float(o[2 * i + 1]) * inv);
+            if (c & 1) {
+              // A lane holds 128 bytes of ONE row: the warp writes its 32 rows as a 128-byte-swizzle box and one
+              // lane hands it to the TMA unit, which writes whole lines and leaves out rows beyond S_q.
+              unsigned char* box = smem + L::kOut + warp * (32 * 128);
+              if (lane == 0) tma_store_wait_read<0>();  // the previous store from this box has read it
+              __syncwarp();
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                *reinterpret_cast<uint4*>(box + lane * 128 + ((j ^ (lane & 7)) << 4)) =
+                    make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
+              fence_proxy_async_smem();
+              __syncwarp();
+              const int row0 = g_row - lane;
+              if (lane == 0 && row0 < p.S_q) {
+                tma_store_3d(&tmap_o, box, (c >> 1) * 64, row0, bh);
+                tma_store_commit();
               }
             }
           }
@@ -567,6 +585,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   }
 
   // ------------------------------------------------------------------ teardown
+  if (!OUT_F32 && warp < 8 && lane == 0) tma_store_wait<0>();  // the output boxes are read and written out
   if (*abort_flag) {
     unsigned long long t0 = globaltimer();
     while (globaltimer() - t0 < 200000ull) __nanosleep(1000);
@@ -597,6 +616,9 @@ int launch_cfg(frisk_b200_ctx* ctx, const frisk_b200_attn_desc& d, const void* Q
   int rc = encode_tmap_3d(ctx, &tq, d.dtype_in, Q, D, d.S_q, bh, row_bytes, row_bytes * d.S_q, 64, BM, 1, true);
   if (!rc) rc = encode_tmap_3d(ctx, &tk, d.dtype_in, K, D, d.S_kv, bh, row_bytes, row_bytes * d.S_kv, 64, BN, 1, true);
   if (!rc) rc = encode_tmap_3d(ctx, &tv, d.dtype_in, V, D, d.S_kv, bh, row_bytes, row_bytes * d.S_kv, 64, BN, 1, true);
+  CUtensorMap to = tq;  // unused for fp32 outputs
+  if (!rc && !OUT_F32)
+    rc = encode_tmap_3d(ctx, &to, d.dtype_out, O, D, d.S_q, bh, row_bytes, row_bytes * d.S_q, 64, 32, 1, true);
   if (rc) {
     ctx->last_cuda = rc;
     return FRISK_B200_E_CUDA;
@@ -633,7 +655,7 @@ int launch_cfg(frisk_b200_ctx* ctx, const frisk_b200_attn_desc& d, const void* Q
   });
   if (bad) return bad;
   const unsigned grid = (unsigned)std::min<int64_t>(p.total_items, ctx->num_sms);
-  kern<<<grid, kThreads, L::kTotal, s>>>(tq, tk, tv, p);
+  kern<<<grid, kThreads, L::kTotal, s>>>(tq, tk, tv, to, p);
   FB_CUDA(ctx, cudaGetLastError());
   return 0;
 }
