@@ -130,7 +130,13 @@ __device__ __forceinline__ Item2 get_item2(int i, int n_full, int num_kb) {
 
 // MODE: what the epilogue does with a finished tile.  Separate instantiations, so that the plain
 // store keeps its register budget and code exactly as if the other two did not exist.
-enum { kStore = 0, kPush = 1, kFused = 2, kStoreTma = 3 };
+enum { kStore = 0, kPush = 1, kFused = 2, kStoreTma = 3, kStoreTmaWide = 4 };
+// kStoreTmaWide: deep-K products.  A work item is a 256 x 512 tile: both accumulators (all 512 tensor-memory columns)
+// belong to ONE item, whose two 256-column halves share every A k-block, so per MMA each SM's shared memory takes
+// 6 KB of TMA writes instead of 8.  The price is that the epilogue no longer overlaps the next item's MMAs, which a
+// long K makes small.  Four stages of 48 KB instead of six of 32 KB.
+constexpr int kWideN = 512;
+constexpr int kStagesWide = 4;
 
 template <typename TO, bool BF16, bool A_MN, bool B_MN, int MODE>
 __global__ void __launch_bounds__(kThreads2, 1)
@@ -140,6 +146,12 @@ __global__ void __launch_bounds__(kThreads2, 1)
                              unsigned* __restrict__ tickets, const PushTargets push, const EpilogueArgs epi,
                              unsigned* __restrict__ status) {
   using L = Smem2;
+  constexpr bool WIDE = MODE == kStoreTmaWide;
+  constexpr bool TMA_OUT = MODE == kStoreTma || MODE == kStoreTmaWide;
+  constexpr int TILE_N = WIDE ? kWideN : BN2;                       // columns of a work item
+  constexpr int NST = WIDE ? kStagesWide : kStages2;                // ring depth
+  constexpr int STAGE = WIDE ? L::kABytes + 2 * L::kBBytes : L::kStageBytes;
+  static_assert(kStagesWide * (L::kABytes + 2 * L::kBBytes) <= L::kBarOffset, "the wide ring must fit in the ring area");
   extern __shared__ unsigned char smem_unaligned[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(
       (reinterpret_cast<uintptr_t>(smem_unaligned) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -155,7 +167,7 @@ __global__ void __launch_bounds__(kThreads2, 1)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();  // 0 = leader
   const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
-  const int tiles_m = (M + BM2 - 1) / BM2, tiles_n = (N + BN2 - 1) / BN2;
+  const int tiles_m = (M + BM2 - 1) / BM2, tiles_n = (N + TILE_N - 1) / TILE_N;
   const int num_kb = (K + BK - 1) / BK;
 
   if (threadIdx.x == 0) {
@@ -172,7 +184,7 @@ __global__ void __launch_bounds__(kThreads2, 1)
     mbar_fence_init();
     tma_prefetch_desc(&tmap_a);
     tma_prefetch_desc(&tmap_b);
-    if (MODE == kStoreTma) tma_prefetch_desc(&tmap_c);
+    if (TMA_OUT) tma_prefetch_desc(&tmap_c);
   }
   if (warp == 1) {
     tmem_alloc_pair(tmem_slot, 512);
@@ -200,16 +212,16 @@ __global__ void __launch_bounds__(kThreads2, 1)
         const Item2 it = get_item2(t, n_full, num_kb);
         TileCoord tc = tile_coord(it.tile, tiles_m, tiles_n);
         const int m0 = tc.m * BM2 + (int)rank * BMC;   // this CTA's rows of A (and of C)
-        const int n0 = tc.n * BN2 + (int)rank * BNC;   // this CTA's half of the B tile
+        const int n0 = tc.n * TILE_N + (int)rank * BNC;   // this CTA's half of the (first) B tile
         for (int kb = it.kb0; kb < it.kb1; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, status, ST_TIMEOUT_EMPTY)) {
             ok = false;
             break;
           }
-          unsigned char* sa = smem + stage * L::kStageBytes;
+          unsigned char* sa = smem + stage * STAGE;
           unsigned char* sb = sa + L::kABytes;
           // the leader's barrier collects the bytes of both CTAs
-          if (rank == 0) mbar_expect_tx(&full_bar[stage], 2 * L::kStageBytes);
+          if (rank == 0) mbar_expect_tx(&full_bar[stage], 2 * STAGE);
           const uint32_t bar = mapa_u32(&full_bar[stage], 0);
           const int k0 = kb * BK;
           if (A_MN) {
@@ -224,7 +236,18 @@ __global__ void __launch_bounds__(kThreads2, 1)
           } else {
             tma_load_2d_pair(sb, &tmap_b, bar, k0, n0);
           }
-          if (++stage == kStages2) {
+          if (WIDE) {
+            // this CTA's half of the second 256 columns (beyond N the TMA unit fills zeros)
+            unsigned char* sb1 = sb + L::kBBytes;
+            if (B_MN) {
+#pragma unroll
+              for (int j = 0; j < BNC / 64; ++j)
+                tma_load_2d_pair(sb1 + j * (BK * 128), &tmap_b, bar, n0 + BN2 + j * 64, k0);
+            } else {
+              tma_load_2d_pair(sb1, &tmap_b, bar, k0, n0 + BN2);
+            }
+          }
+          if (++stage == NST) {
             stage = 0;
             phase ^= 1;
           }
@@ -244,14 +267,14 @@ __global__ void __launch_bounds__(kThreads2, 1)
         const Item2 it = get_item2(t, n_full, num_kb);
         if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag, status, ST_TIMEOUT_ACC_EMPTY)) break;
         tc_fence_after_sync();
-        const uint32_t d_tmem = tmem_base + acc * BN2;
+        const uint32_t d_tmem = tmem_base + (WIDE ? 0 : acc * BN2);
         for (int kb = it.kb0; kb < it.kb1; ++kb) {
           if (!mbar_wait(&full_bar[stage], phase, abort_flag, status, ST_TIMEOUT_FULL)) {
             ok = false;
             break;
           }
           tc_fence_after_sync();
-          const uint32_t sa = smem_u32(smem + stage * L::kStageBytes);
+          const uint32_t sa = smem_u32(smem + stage * STAGE);
           const uint32_t sb = sa + L::kABytes;
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
@@ -260,16 +283,24 @@ __global__ void __launch_bounds__(kThreads2, 1)
             uint64_t db = B_MN ? umma_desc_mnmajor_sw128(sb + k * (UMMA_K * 128), BK * 128, 1024)
                                : umma_desc_kmajor_sw128(sb + k * (UMMA_K * 2));
             umma_f16_ss_pair(d_tmem, da, db, idesc, (kb > it.kb0 || k != 0) ? 1u : 0u);
+            if (WIDE) {
+              const uint32_t sb1 = sb + L::kBBytes;
+              uint64_t db1 = B_MN ? umma_desc_mnmajor_sw128(sb1 + k * (UMMA_K * 128), BK * 128, 1024)
+                                  : umma_desc_kmajor_sw128(sb1 + k * (UMMA_K * 2));
+              umma_f16_ss_pair(d_tmem + BN2, da, db1, idesc, (kb > it.kb0 || k != 0) ? 1u : 0u);
+            }
           }
           umma_commit_pair(&empty_bar[stage], 3);  // both CTAs may refill this stage
-          if (++stage == kStages2) {
+          if (++stage == NST) {
             stage = 0;
             phase ^= 1;
           }
         }
         if (!ok) break;
         umma_commit_pair(&acc_full[acc], 3);  // both CTAs' epilogues may read their accumulator halves
-        if (++acc == 2) {
+        if (WIDE) {
+          acc_phase ^= 1;  // one accumulator (of 512 columns), used by every item
+        } else if (++acc == 2) {
           acc = 0;
           acc_phase ^= 1;
         }
@@ -293,12 +324,12 @@ __global__ void __launch_bounds__(kThreads2, 1)
     for (int t = pair; t < n_items; t += num_pairs) {
       const Item2 it = get_item2(t, n_full, num_kb);
       TileCoord tc = tile_coord(it.tile, tiles_m, tiles_n);
-      const int m0 = tc.m * BM2 + (int)rank * BMC, n0 = tc.n * BN2;
+      const int m0 = tc.m * BM2 + (int)rank * BMC, n0 = tc.n * TILE_N;
       if (!mbar_wait(&acc_full[acc], acc_phase, abort_flag, status, ST_TIMEOUT_ACC_FULL)) break;
       tc_fence_after_sync();
       const int row_local = quad * 32 + lane;
       const int row = m0 + row_local;
-      const uint32_t taddr = tmem_base + acc * BN2 + (static_cast<uint32_t>(quad * 32) << 16);
+      const uint32_t taddr = tmem_base + (WIDE ? 0 : acc * BN2) + (static_cast<uint32_t>(quad * 32) << 16);
       bool write_c = true;
       const float4* other = nullptr;
       if (it.tail >= 0) {  // (pushed K halves simply both add into the owner's buffer)
@@ -331,14 +362,14 @@ __global__ void __launch_bounds__(kThreads2, 1)
       if (MODE == kFused)
         row_acc = epi.reduce_kind == FRISK_B200_REDUCE_MAX ? -INFINITY
                   : epi.reduce_kind == FRISK_B200_REDUCE_MIN ? INFINITY : 0.f;
-      if (MODE == kStoreTma && write_c) {
+      if (TMA_OUT && write_c) {
         // Plain store through shared memory: a lane holds 128 bytes of ONE row, the warp writes them as a
         // [32 rows][128 bytes] box in the 128-byte-swizzle image and one lane hands the box to the TMA unit,
         // which writes whole lines and clips the box at the edges of C.  Two boxes per warp alternate.
         constexpr int kUnitCols = 128 / (int)sizeof(TO);
         unsigned char* boxes = smem + L::kOutOffset + quad * L::kOutWarpBytes;
 #pragma unroll 1
-        for (int u = 0; u < BN2 / kUnitCols; ++u) {
+        for (int u = 0; u < TILE_N / kUnitCols; ++u) {
           const int c0 = n0 + u * kUnitCols, r0 = m0 + quad * 32;
           if (c0 >= N || r0 >= M) break;  // wholly outside C (warp-uniform)
           uint32_t w[32];
@@ -466,12 +497,14 @@ __global__ void __launch_bounds__(kThreads2, 1)
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(acc ? leader_acc_empty1 : leader_acc_empty0);
-      if (++acc == 2) {
+      if (WIDE) {
+        acc_phase ^= 1;
+      } else if (++acc == 2) {
         acc = 0;
         acc_phase ^= 1;
       }
     }
-    if (MODE == kStoreTma && lane == 0) tma_store_wait<0>();  // the boxes are read and written out before the CTA leaves
+    if (TMA_OUT && lane == 0) tma_store_wait<0>();  // the boxes are read and written out before the CTA leaves
   }
 
   // ------------------------------------------------------------------ teardown
@@ -536,7 +569,7 @@ int launch_cfg2(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc& d, const void* 
   if (rc) { ctx->last_cuda = rc; return FRISK_B200_E_CUDA; }
 
   CUtensorMap tc = ta;  // unused by the other modes
-  if (MODE == kStoreTma) {
+  if (MODE == kStoreTma || MODE == kStoreTmaWide) {
     // C as [M][N] with boxes of 32 rows x 128 bytes in the 128-byte-swizzle image the epilogue writes
     const int out_dtype = sizeof(TO) == 4 ? FRISK_B200_F32 : (std::is_same<TO, __half>::value ? FRISK_B200_F16 : FRISK_B200_BF16);
     rc = encode_tmap_2d(ctx, &tc, out_dtype, C, (uint64_t)g.N, (uint64_t)g.M, (uint64_t)g.ldc * sizeof(TO),
@@ -545,7 +578,8 @@ int launch_cfg2(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc& d, const void* 
   }
 
   auto kern = gemm_tcgen05_2cta_kernel<TO, BF16, A_MN, B_MN, MODE>;
-  constexpr int kSmemBytes = MODE == kPush ? Smem2::kTotalPush : MODE == kStoreTma ? Smem2::kTotalOut : Smem2::kTotal;
+  constexpr int kSmemBytes = MODE == kPush ? Smem2::kTotalPush
+                             : (MODE == kStoreTma || MODE == kStoreTmaWide) ? Smem2::kTotalOut : Smem2::kTotal;
   cudaLaunchConfig_t cfg = {};
   cudaLaunchAttribute attr[2];
   attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -580,6 +614,14 @@ int launch_cfg2(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc& d, const void* 
   if (push_in) push = *push_in;
   EpilogueArgs epi{};
   if (epi_in) epi = *epi_in;
+  if (MODE == kStoreTmaWide) {
+    // 256 x 512 items, every one whole
+    const int tiles_w = (int)(((g.M + BM2 - 1) / BM2) * ((g.N + kWideN - 1) / kWideN));
+    tp.pairs = tiles_w < max_clusters ? tiles_w : max_clusters;
+    tp.n_full = tp.n_items = tiles_w;
+    tp.tail_tiles = 0;
+    tp.bytes = 0;
+  }
   if (tp.bytes && (MODE == kPush || !ws || ws_bytes < tp.bytes)) {
     // no scratch: run every tile whole
     tp.n_full = tp.n_items = tp.n_full + tp.tail_tiles;
@@ -659,6 +701,15 @@ int launch_gemm_tcgen05_2cta(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc& d,
   const size_t cs = dtype_size(d.dtype_c);
 #ifndef FB_NO_TMA_STORE
   if (d.clear_accum && aligned16(C) && (g.ldc * cs) % 16 == 0) {
+    // deep K and enough 256 x 512 items to keep every CTA pair busy for several rounds: the wide items
+    const int64_t tiles_w = ((g.M + BM2 - 1) / BM2) * ((g.N + kWideN - 1) / kWideN);
+    if (g.K >= 8192 && tiles_w >= 4 * kPairsAssumed) {
+      if (d.dtype_c == FRISK_B200_F32)
+        return bf ? launch_major2<float, true, kStoreTmaWide>(ctx, d, A, B, C, ws, ws_bytes, s, nullptr)
+                  : launch_major2<float, false, kStoreTmaWide>(ctx, d, A, B, C, ws, ws_bytes, s, nullptr);
+      if (bf) return launch_major2<__nv_bfloat16, true, kStoreTmaWide>(ctx, d, A, B, C, ws, ws_bytes, s, nullptr);
+      return launch_major2<__half, false, kStoreTmaWide>(ctx, d, A, B, C, ws, ws_bytes, s, nullptr);
+    }
     if (d.dtype_c == FRISK_B200_F32)
       return bf ? launch_major2<float, true, kStoreTma>(ctx, d, A, B, C, ws, ws_bytes, s, nullptr)
                 : launch_major2<float, false, kStoreTma>(ctx, d, A, B, C, ws, ws_bytes, s, nullptr);

@@ -234,6 +234,36 @@ def test_tc_config_4096_nt(ctx):
     assert rel_frobenius(from_storage(got, "fp16"), lib) <= TOL["fp16"]
 
 
+@pytest.mark.parametrize("tb,dtype_c", [(True, "bf16"), (False, "fp32")])
+def test_tc_pair_wide_items_deep_k(ctx, tb, dtype_c):
+    """K >= 8192 with several rounds of 256 x 512 items per CTA pair: both accumulators belong to one item whose
+    halves share the A k-blocks.  Ragged M and N (the last item's second half lies wholly beyond N); the fp64
+    oracle covers sampled rows, the first and the last 128 rows, over all columns."""
+    import torch
+    M, N, K = 4700, 8200, 8192
+    a, b = inputs.gemm_inputs(M, N, K, "bf16", False, tb, 51, "normal_rsqrt_k")
+    da, db = to_device(a, "bf16"), to_device(b, "bf16")
+    dc = torch.full((M, N), float("nan"), dtype=torch.bfloat16 if dtype_c == "bf16" else torch.float32, device="cuda")
+    desc = capi.gemm_desc(M, N, K, "bf16", dtype_c, False, tb, clear_accum=True)
+    assert capi.load().frisk_b200_gemm_select(desc) == capi.ALGO_TCGEN05_PAIR
+    stream = torch.cuda.current_stream().cuda_stream
+    ctx.gemm(desc, da.data_ptr(), db.data_ptr(), dc.data_ptr(), stream=stream)
+    ctx.check(stream)
+    got = from_storage(to_host(dc, dtype_c), dtype_c)
+    assert np.isfinite(got).all()
+    rng = np.random.default_rng(52)
+    rows = np.unique(np.concatenate([rng.choice(M, 64, replace=False), np.arange(128), np.arange(M - 128, M)]))
+    a64 = from_storage(a, "bf16").astype(np.float64)[rows]
+    b64 = from_storage(b, "bf16").astype(np.float64)
+    ref = a64 @ (b64.T if tb else b64)
+    err = rel_frobenius(got[rows], ref)
+    assert err <= TOL["bf16"], err
+    again = torch.full_like(dc, float("nan"))
+    ctx.gemm(desc, da.data_ptr(), db.data_ptr(), again.data_ptr(), stream=stream)
+    ctx.check(stream)
+    assert torch.equal(dc, again)
+
+
 def test_deepk_config(ctx):
     """bf16 GEMM M = N = 8192, K = 131072 at its own size (2048 k-blocks per tile, 1024 tiles on 74 CTA
     pairs, both tensor-memory accumulators).  The whole product is 17.6 TFLOP, out of reach for a
