@@ -37,6 +37,7 @@ constexpr int UMMA_K = 16;
 constexpr int kStages2 = 6;
 constexpr int kThreads2 = 192;
 constexpr size_t kTicketBytes = 1024;
+constexpr int kMinKbAllHalved = 16;  // k-blocks a product needs before halving every tile's K pays for the fp32 hand-over
 constexpr int kPairsAssumed = kNumSMsDefault / 2;  // CTA pairs the tail plan (and its workspace size) is made for
 
 struct Smem2 {
@@ -542,6 +543,12 @@ TailPlan make_tail_plan(const frisk_b200_gemm_desc& d, int pairs_available) {
     t.tail_tiles = rem;
     t.n_full = tiles - rem;
     t.n_items = t.n_full + 2 * rem;
+  } else if (2 * tiles <= pairs_available && num_kb >= kMinKbAllHalved) {
+    // fewer tiles than half the pairs: EVERY tile runs as two K halves, so twice as many SMs work
+    t.tail_tiles = tiles;
+    t.n_full = 0;
+    t.n_items = 2 * tiles;
+    t.pairs = 2 * tiles;
   }
   // tickets live in a fixed-size prefix so that a scratch buffer reused for another shape never
   // finds old partial sums where it keeps tickets
@@ -657,9 +664,12 @@ int launch_major2(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc& d, const void
 }  // namespace
 
 // The pair kernel pays when there are enough 256 x 256 tiles to fill the machine's CTA pairs.
+// ... or so few that halving every tile's K doubles the SMs at work (the one-CTA kernel's 128 x 256 tiles
+// would occupy at most as many SMs as there are tiles x 2).
 bool tcgen05_2cta_preferred(const frisk_b200_gemm_desc& d) {
   const int64_t tiles = ((d.M + BM2 - 1) / BM2) * ((d.N + BN2 - 1) / BN2);
-  return tiles >= kNumSMsDefault / 2;
+  if (tiles >= kNumSMsDefault / 2) return true;
+  return 2 * tiles <= kPairsAssumed && (d.K + BK - 1) / BK >= kMinKbAllHalved;
 }
 
 // Split-K across GPUs: the same kernel, its epilogue storing every fp32 tile into this rank's slot at the row's owner.
@@ -680,7 +690,9 @@ int tcgen05_2cta_column_tiles(const frisk_b200_gemm_desc& d) { return (int)((res
 size_t tcgen05_2cta_workspace_bytes(const frisk_b200_gemm_desc& d) {
   GemmDims g = resolve_dims(d);
   const int64_t tiles = ((g.M + BM2 - 1) / BM2) * ((g.N + BN2 - 1) / BN2);
-  if (tiles <= kPairsAssumed / 2 || (g.K + BK - 1) / BK < 8) return 0;
+  const int64_t num_kb = (g.K + BK - 1) / BK;
+  if (num_kb < 8) return 0;
+  if (2 * tiles <= kPairsAssumed ? num_kb < kMinKbAllHalved : tiles <= kPairsAssumed) return 0;
   return kTicketBytes + (size_t)(kPairsAssumed / 2) * 2 * BM2 * BN2 * sizeof(float);
 }
 

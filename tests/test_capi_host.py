@@ -74,13 +74,17 @@ def test_kernel_selection_and_workspace():
     assert sel(capi.gemm_desc(64, 64, 64, "fp32", algo=6)) == -7
     assert sel(capi.gemm_desc(4096, 4096, 4096, "fp16", trans_b=True)) == capi.ALGO_TCGEN05_PAIR
     assert sel(capi.gemm_desc(4096, 4096, 4096, "fp16")) == capi.ALGO_TCGEN05_PAIR
-    assert sel(capi.gemm_desc(1024, 1024, 4096, "fp16", trans_b=True)) == capi.ALGO_TCGEN05  # too few 256x256 tiles for pairs
+    # 16 tiles of 256x256: every tile as two K halves on 32 CTA pairs rather than 32 one-CTA tiles
+    assert sel(capi.gemm_desc(1024, 1024, 4096, "fp16", trans_b=True)) == capi.ALGO_TCGEN05_PAIR
+    assert sel(capi.gemm_desc(1024, 1024, 512, "fp16", trans_b=True)) == capi.ALGO_TCGEN05   # K too short to halve
+    assert sel(capi.gemm_desc(2048, 1792, 4096, "fp16", trans_b=True)) == capi.ALGO_TCGEN05  # 56 tiles: one CTA each
     skinny = capi.gemm_desc(16, 28672, 8192, "bf16", trans_b=True)
     assert sel(skinny) == capi.ALGO_SKINNY
     assert lib.frisk_b200_gemm_workspace_bytes(skinny) > 0
     # the CTA-pair kernel may split the K extent of a partial last wave: scratch for its fp32 halves
     assert lib.frisk_b200_gemm_workspace_bytes(capi.gemm_desc(4096, 4096, 4096, "fp16", trans_b=True)) > 0
-    assert lib.frisk_b200_gemm_workspace_bytes(capi.gemm_desc(1024, 1024, 4096, "fp16", trans_b=True)) == 0
+    assert lib.frisk_b200_gemm_workspace_bytes(capi.gemm_desc(1024, 1024, 4096, "fp16", trans_b=True)) > 0
+    assert lib.frisk_b200_gemm_workspace_bytes(capi.gemm_desc(2048, 1792, 4096, "fp16", trans_b=True)) == 0
     assert lib.frisk_b200_gemm_workspace_bytes(capi.gemm_desc(1024, 1024, 1024, "fp32")) == 0
     assert sel(capi.gemm_desc(16, 64, 64, "bf16")) == capi.ALGO_TCGEN05  # weights not K-contiguous
     assert sel(capi.gemm_desc(64, 64, 60, "bf16", trans_b=True)) == -3   # 120-byte pitch

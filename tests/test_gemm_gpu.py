@@ -193,6 +193,18 @@ def test_tc_store_boxes_at_ragged_edges(ctx, algo, dtype_c):
 
 
 @pytest.mark.parametrize("tb", [True, False])
+def test_tc_pair_few_tiles_all_split_in_k(ctx, tb):
+    """Fewer 256 x 256 tiles than half the CTA pairs and a K worth halving: EVERY tile runs as two K halves that
+    meet through the fp32 scratch (ragged edges, fp32 and 16-bit outputs, accumulate, repeat on the same scratch)."""
+    P = capi.ALGO_TCGEN05_PAIR
+    for _ in range(2):
+        check(ctx, 1024, 2048, 4096, "fp16", "fp16", False, tb, 61, algo=capi.ALGO_AUTO, dist="normal_rsqrt_k")
+    check(ctx, 1000, 1800, 2048, "bf16", "fp32", False, tb, 62, algo=P, dist="normal_rsqrt_k")
+    check(ctx, 520, 304, 1024, "bf16", "bf16", False, tb, 63, accumulate=True, algo=P, dist="normal_rsqrt_k")
+    check(ctx, 256, 256, 8192, "fp16", "fp16", False, tb, 64, algo=capi.ALGO_AUTO, dist="normal_rsqrt_k")
+
+
+@pytest.mark.parametrize("tb", [True, False])
 def test_tc_pair_tail_wave_split_in_k(ctx, tb):
     # 8 x 10 = 80 tiles of 256x256 on 74 CTA pairs: the 6 tiles of the last wave run as 12 K halves
     # that meet through the fp32 scratch
