@@ -131,8 +131,8 @@ __device__ __forceinline__ Item2 get_item2(int i, int n_full, int num_kb) {
 
 // MODE: what the epilogue does with a finished tile.  Separate instantiations, so that the plain
 // store keeps its register budget and code exactly as if the other two did not exist.
-enum { kStore = 0, kPush = 1, kFused = 2, kStoreTma = 3, kStoreTmaWide = 4 };
-// kStoreTmaWide: deep-K products.  A work item is a 256 x 512 tile: both accumulators (all 512 tensor-memory columns)
+enum { kStore = 0, kPush = 1, kFused = 2, kStoreTma = 3, kStoreTmaWide = 4, kPushWide = 5 };
+// kStoreTmaWide, kPushWide: deep-K products.  A work item is a 256 x 512 tile: both accumulators (all 512 tensor-memory columns)
 // belong to ONE item, whose two 256-column halves share every A k-block, so per MMA each SM's shared memory takes
 // 6 KB of TMA writes instead of 8.  The price is that the epilogue no longer overlaps the next item's MMAs, which a
 // long K makes small.  Four stages of 48 KB instead of six of 32 KB.
@@ -147,7 +147,8 @@ __global__ void __launch_bounds__(kThreads2, 1)
                              unsigned* __restrict__ tickets, const PushTargets push, const EpilogueArgs epi,
                              unsigned* __restrict__ status) {
   using L = Smem2;
-  constexpr bool WIDE = MODE == kStoreTmaWide;
+  constexpr bool WIDE = MODE == kStoreTmaWide || MODE == kPushWide;
+  constexpr bool PUSH = MODE == kPush || MODE == kPushWide;
   constexpr bool TMA_OUT = MODE == kStoreTma || MODE == kStoreTmaWide;
   constexpr int TILE_N = WIDE ? kWideN : BN2;                       // columns of a work item
   constexpr int NST = WIDE ? kStagesWide : kStages2;                // ring depth
@@ -426,7 +427,7 @@ __global__ void __launch_bounds__(kThreads2, 1)
         }
       } else if (write_c) {
 #pragma unroll 1
-        for (int c = 0; c < BN2 / 32; ++c) {
+        for (int c = 0; c < TILE_N / 32; ++c) {
           uint32_t v[32];
           tmem_ld_32x32b_x32(taddr + c * 32, v);
           tmem_ld_wait();
@@ -441,7 +442,7 @@ __global__ void __launch_bounds__(kThreads2, 1)
             }
           }
           const int col = n0 + c * 32;
-          if (MODE == kPush) {
+          if (PUSH) {
             // split-K across GPUs: store this chunk into this rank's slot at the GPU that owns the row.
             // A thread holds 32 columns of ONE row; stored as they are, every 16-byte store would be
             // its own NVLink transaction (measured: 65 GB/s per GPU).  The warp therefore transposes
@@ -585,7 +586,7 @@ int launch_cfg2(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc& d, const void* 
   }
 
   auto kern = gemm_tcgen05_2cta_kernel<TO, BF16, A_MN, B_MN, MODE>;
-  constexpr int kSmemBytes = MODE == kPush ? Smem2::kTotalPush
+  constexpr int kSmemBytes = (MODE == kPush || MODE == kPushWide) ? Smem2::kTotalPush
                              : (MODE == kStoreTma || MODE == kStoreTmaWide) ? Smem2::kTotalOut : Smem2::kTotal;
   cudaLaunchConfig_t cfg = {};
   cudaLaunchAttribute attr[2];
@@ -621,7 +622,7 @@ int launch_cfg2(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc& d, const void* 
   if (push_in) push = *push_in;
   EpilogueArgs epi{};
   if (epi_in) epi = *epi_in;
-  if (MODE == kStoreTmaWide) {
+  if (MODE == kStoreTmaWide || MODE == kPushWide) {
     // 256 x 512 items, every one whole
     const int tiles_w = (int)(((g.M + BM2 - 1) / BM2) * ((g.N + kWideN - 1) / kWideN));
     tp.pairs = tiles_w < max_clusters ? tiles_w : max_clusters;
@@ -629,7 +630,7 @@ int launch_cfg2(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc& d, const void* 
     tp.tail_tiles = 0;
     tp.bytes = 0;
   }
-  if (tp.bytes && (MODE == kPush || !ws || ws_bytes < tp.bytes)) {
+  if (tp.bytes && (MODE == kPush || MODE == kPushWide || !ws || ws_bytes < tp.bytes)) {
     // no scratch: run every tile whole
     tp.n_full = tp.n_items = tp.n_full + tp.tail_tiles;
     tp.tail_tiles = 0;
@@ -679,6 +680,14 @@ int launch_gemm_tcgen05_2cta_push(frisk_b200_ctx* ctx, const frisk_b200_gemm_des
   if (!aligned16(A) || !aligned16(B)) return FRISK_B200_E_ALIGN;
   const bool a_mn = d.trans_a != 0, b_mn = d.trans_b == 0;
   if (a_mn || b_mn) return FRISK_B200_E_UNSUPPORTED;  // the K-split path keeps both operands K-contiguous
+  // deep K and several rounds of 256 x 512 items per CTA pair: the wide items (see kStoreTmaWide)
+  const GemmDims g = resolve_dims(d);
+  const int64_t tiles_w = ((g.M + BM2 - 1) / BM2) * ((g.N + kWideN - 1) / kWideN);
+  if (g.K >= 8192 && tiles_w >= 4 * kPairsAssumed) {
+    if (d.dtype_ab == FRISK_B200_BF16)
+      return launch_cfg2<float, true, false, false, kPushWide>(ctx, d, A, B, nullptr, nullptr, 0, s, &push);
+    return launch_cfg2<float, false, false, false, kPushWide>(ctx, d, A, B, nullptr, nullptr, 0, s, &push);
+  }
   if (d.dtype_ab == FRISK_B200_BF16)
     return launch_cfg2<float, true, false, false, kPush>(ctx, d, A, B, nullptr, nullptr, 0, s, &push);
   return launch_cfg2<float, false, false, false, kPush>(ctx, d, A, B, nullptr, nullptr, 0, s, &push);

@@ -461,6 +461,29 @@ def test_gemm_push_into_row_block_owners(ctx):
         ctx.gemm_push(desc, da.data_ptr(), db.data_ptr(), [owners[0][0].data_ptr()], M // 4, N, stream=s)  # rows not covered
 
 
+def test_gemm_push_wide_items_deep_k(ctx):
+    """The K-split push with K >= 8192 per rank and several rounds of 256 x 512 items per CTA pair (the shape class of
+    the deep-K benchmark split over GPUs): two K halves pushed into two row-block owners, ragged N."""
+    import torch
+    M, N, K = 4608, 8200, 16384
+    a, b = inputs.gemm_inputs(M, N, K, "bf16", False, True, 65, "normal_rsqrt_k")
+    rows = M // 2
+    owners = [torch.full((2, rows, N), float("nan"), device="cuda") for _ in range(2)]
+    desc = capi.gemm_desc(M, N, K // 2, "bf16", "fp32", False, True, clear_accum=True, algo=capi.ALGO_TCGEN05_PAIR)
+    s = torch.cuda.current_stream().cuda_stream
+    for rank in range(2):
+        da = to_device(np.ascontiguousarray(a[:, rank * (K // 2):(rank + 1) * (K // 2)]), "bf16")
+        db = to_device(np.ascontiguousarray(b[:, rank * (K // 2):(rank + 1) * (K // 2)]), "bf16")
+        ctx.gemm_push(desc, da.data_ptr(), db.data_ptr(), [o[rank].data_ptr() for o in owners], rows, N, stream=s)
+    ctx.check(s)
+    got = torch.cat([o.sum(dim=0) for o in owners]).cpu().numpy()
+    assert np.isfinite(got).all()
+    rng = np.random.default_rng(66)
+    pick = np.unique(np.concatenate([rng.choice(M, 48, replace=False), np.arange(32), np.arange(M - 32, M)]))
+    ref = from_storage(a, "bf16").astype(np.float64)[pick] @ from_storage(b, "bf16").astype(np.float64).T
+    assert rel_frobenius(got[pick], ref) <= 1e-5
+
+
 def test_gemm_push_more_tiles_than_cta_pairs(ctx):
     # 80 tiles on 74 CTA pairs, four owners: every tile is stored whole (no K halves in this mode)
     import torch
