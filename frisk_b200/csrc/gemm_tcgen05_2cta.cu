@@ -680,10 +680,12 @@ int launch_gemm_tcgen05_2cta_push(frisk_b200_ctx* ctx, const frisk_b200_gemm_des
   if (!aligned16(A) || !aligned16(B)) return FRISK_B200_E_ALIGN;
   const bool a_mn = d.trans_a != 0, b_mn = d.trans_b == 0;
   if (a_mn || b_mn) return FRISK_B200_E_UNSUPPORTED;  // the K-split path keeps both operands K-contiguous
-  // deep K and several rounds of 256 x 512 items per CTA pair: the wide items (see kStoreTmaWide)
+  // very deep K and several rounds of 256 x 512 items per CTA pair: the wide items (see kStoreTmaWide).  The push
+  // of a wide item (512 KB per CTA to the row owners) does not hide behind the next item, so the bar is higher than
+  // for a local store: 8192 x 8192 with K = 65536 per rank gains 6 %, with K = 16384 per rank it loses 2 %.
   const GemmDims g = resolve_dims(d);
   const int64_t tiles_w = ((g.M + BM2 - 1) / BM2) * ((g.N + kWideN - 1) / kWideN);
-  if (g.K >= 8192 && tiles_w >= 4 * kPairsAssumed) {
+  if (g.K >= 32768 && tiles_w >= 4 * kPairsAssumed) {
     if (d.dtype_ab == FRISK_B200_BF16)
       return launch_cfg2<float, true, false, false, kPushWide>(ctx, d, A, B, nullptr, nullptr, 0, s, &push);
     return launch_cfg2<float, false, false, false, kPushWide>(ctx, d, A, B, nullptr, nullptr, 0, s, &push);

@@ -462,10 +462,10 @@ def test_gemm_push_into_row_block_owners(ctx):
 
 
 def test_gemm_push_wide_items_deep_k(ctx):
-    """The K-split push with K >= 8192 per rank and several rounds of 256 x 512 items per CTA pair (the shape class of
-    the deep-K benchmark split over GPUs): two K halves pushed into two row-block owners, ragged N."""
+    """The K-split push with K >= 32768 per rank and several rounds of 256 x 512 items per CTA pair (the shape class of
+    the deep-K benchmark split over two or four GPUs): two K halves pushed into two row-block owners, ragged N."""
     import torch
-    M, N, K = 4608, 8200, 16384
+    M, N, K = 4608, 8200, 65536
     a, b = inputs.gemm_inputs(M, N, K, "bf16", False, True, 65, "normal_rsqrt_k")
     rows = M // 2
     owners = [torch.full((2, rows, N), float("nan"), device="cuda") for _ in range(2)]
@@ -481,7 +481,7 @@ def test_gemm_push_wide_items_deep_k(ctx):
     rng = np.random.default_rng(66)
     pick = np.unique(np.concatenate([rng.choice(M, 48, replace=False), np.arange(32), np.arange(M - 32, M)]))
     ref = from_storage(a, "bf16").astype(np.float64)[pick] @ from_storage(b, "bf16").astype(np.float64).T
-    assert rel_frobenius(got[pick], ref) <= 1e-5
+    assert rel_frobenius(got[pick], ref) <= 1e-4   # fp32 sums of 32768 products per rank, unrounded output
 
 
 def test_gemm_push_more_tiles_than_cta_pairs(ctx):
