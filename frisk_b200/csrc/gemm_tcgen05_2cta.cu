@@ -726,6 +726,7 @@ int launch_gemm_tcgen05_2cta(frisk_b200_ctx* ctx, const frisk_b200_gemm_desc& d,
   if (d.clear_accum && aligned16(C) && (g.ldc * cs) % 16 == 0) {
     // deep K and enough 256 x 512 items to keep every CTA pair busy for several rounds: the wide items
     const int64_t tiles_w = ((g.M + BM2 - 1) / BM2) * ((g.N + kWideN - 1) / kWideN);
+    // (at 8192 x 8192 the wide items lose 2-7 % for K <= 4096, where the exposed epilogue outweighs the saved writes)
     if (g.K >= 8192 && tiles_w >= 4 * kPairsAssumed) {
       if (d.dtype_c == FRISK_B200_F32)
         return bf ? launch_major2<float, true, kStoreTmaWide>(ctx, d, A, B, C, ws, ws_bytes, s, nullptr)
