@@ -63,6 +63,34 @@ def ncu_traffic(key):
 
 
 # ----------------------------------------------------------------------------- clocks
+def bind_to_gpu_numa(gpu_index):
+    """Restricts this process to the CPUs NVML reports as local to its GPU (a read-only query), before any pinned
+    buffer is allocated, so that the buffers are first touched on the GPU's own NUMA node.  Only with more than one
+    rank; returns what it did for the JSON line."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+        index = gpu_index
+        if visible:
+            ids = [v.strip() for v in visible.split(",") if v.strip()]
+            if gpu_index < len(ids) and ids[gpu_index].isdigit():
+                index = int(ids[gpu_index])
+        handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+        ncpu = os.cpu_count() or 1
+        words = pynvml.nvmlDeviceGetCpuAffinity(handle, (ncpu + 63) // 64)
+        local = {64 * w + b for w, word in enumerate(words) for b in range(64) if (int(word) >> b) & 1}
+        allowed = os.sched_getaffinity(0)
+        target = local & allowed
+        if not target:
+            return {"bound": False, "why": "no allowed CPU is local to the GPU"}
+        if target != allowed:
+            os.sched_setaffinity(0, target)
+        return {"bound": True, "local_cpus": len(target), "allowed_before": len(allowed)}
+    except Exception as e:  # noqa: BLE001
+        return {"bound": False, "why": str(e)[:80]}
+
+
 class ClockSampler:
     """Samples the SM clock and the throttle reasons through NVML (read-only queries) every few
     milliseconds while the timed region runs; falls back to one nvidia-smi query if NVML is
@@ -253,6 +281,7 @@ def run_ours(args):
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the kernels have no CPU path")
     torch.cuda.set_device(local)
+    numa = bind_to_gpu_numa(local) if world > 1 else None
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     ctx = capi.Context(local)
@@ -321,6 +350,8 @@ def run_ours(args):
     e2e_err = rel_err_gemm_sample(torch, sets[0][0], sets[0][1], hc.cuda(), sample_indices(M, 64, 15),
                                   sample_indices(N, 256, 16))
     link = host_link_rates(torch, dist, world, ha, hc)
+    if numa is not None:
+        link["numa"] = numa
 
     splitk_res = sharded_res = None
     if world > 1 and not args.no_secondary:
