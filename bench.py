@@ -55,7 +55,7 @@ def measured_peaks():
 
 # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures
 # summarised under profiles/ (one file per kernel and workload).
-NCU_TRAFFIC = {"gemm_tcgen05_f16_4096": 101886464, "gemm_skinny_bf16_16x28672x8192": 478497792}
+NCU_TRAFFIC = {"gemm_tcgen05_f16_4096": 111135744, "gemm_skinny_bf16_16x28672x8192": 478497792}
 
 
 def ncu_traffic(key):
